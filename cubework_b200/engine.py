@@ -1,0 +1,110 @@
+"""Training engine: the call a user makes to run one optimisation step.
+
+Parity: the ``_train`` hot loop of benchmark/{gpt2,opt,vit}/train.py:44-184 — micro-batch loop with
+gradient accumulation, autocast forward, loss, backward, gradient clipping, optimizer + scheduler step,
+``zero_grad``.  Differences: inputs are copied host->device from pinned memory on a side stream one
+step ahead; bf16 needs no ``GradScaler`` (fp16 still gets one); there is no per-micro-batch host
+synchronisation — ``step`` returns the loss as a device tensor and ``loss.item()`` is the caller's
+choice.
+"""
+import contextlib
+
+import torch
+
+from .parallel.common import synchronize as _sync_async_grads
+from .utils.clip_grad import clip_grad_norm
+
+
+class Trainer:
+
+    def __init__(self, model, criterion, optimizer, lr_scheduler=None, *, amp_dtype=torch.bfloat16, clip=None,
+                 accum_steps=1, forward_fn=None, device=None):
+        """``forward_fn(model, batch) -> (outputs, targets)``; default feeds ``batch`` as kwargs minus
+        ``labels`` and uses ``batch["labels"]`` as targets."""
+        self.model, self.criterion, self.optimizer, self.lr_scheduler = model, criterion, optimizer, lr_scheduler
+        self.amp_dtype, self.clip, self.accum_steps = amp_dtype, clip, accum_steps
+        self.forward_fn = forward_fn or self._default_forward
+        self.device = device or next(model.parameters()).device
+        self.scaler = torch.amp.GradScaler("cuda") if (amp_dtype == torch.float16 and self.device.type == "cuda") \
+            else None
+        self._copy_stream = torch.cuda.Stream() if self.device.type == "cuda" else None
+        self.h2d_bytes = 0
+        self.steps = 0
+
+    @staticmethod
+    def _default_forward(model, batch):
+        labels = batch["labels"]
+        out = model(**{k: v for k, v in batch.items() if k != "labels"})
+        if isinstance(out, tuple):
+            out = out[0]
+        return out, labels
+
+    def to_device(self, batch):
+        """Asynchronous host->device copy of a dict of (pinned) host tensors."""
+        if self.device.type != "cuda":
+            return batch
+        out = {}
+        with torch.cuda.stream(self._copy_stream):
+            for k, v in batch.items():
+                if torch.is_tensor(v) and v.device.type == "cpu":
+                    self.h2d_bytes += v.numel() * v.element_size()
+                    out[k] = v.to(self.device, non_blocking=True)
+                else:
+                    out[k] = v
+        torch.cuda.current_stream().wait_stream(self._copy_stream)
+        for v in out.values():
+            if torch.is_tensor(v):
+                v.record_stream(torch.cuda.current_stream())
+        return out
+
+    def _autocast(self):
+        if self.amp_dtype is None or self.device.type != "cuda":
+            return contextlib.nullcontext()
+        return torch.autocast("cuda", dtype=self.amp_dtype)
+
+    def step(self, batches):
+        """One optimisation step over ``accum_steps`` micro-batches (a dict, or a list of dicts)."""
+        if isinstance(batches, dict):
+            batches = [batches]
+        self.model.train()
+        total = None
+        n = len(batches)
+        for i, batch in enumerate(batches):
+            batch = self.to_device(batch)
+            sync_ctx = contextlib.nullcontext()
+            if i < n - 1 and hasattr(self.model, "no_sync"):
+                sync_ctx = self.model.no_sync()
+            with sync_ctx:
+                with self._autocast():
+                    out, targets = self.forward_fn(self.model, batch)
+                    loss = self.criterion(out, targets)
+                scaled = loss / n if n > 1 else loss
+                if self.scaler is not None:
+                    self.scaler.scale(scaled).backward()
+                else:
+                    scaled.backward()
+            total = loss.detach() if total is None else total + loss.detach()
+        _sync_async_grads()
+        if self.scaler is not None:
+            self.scaler.unscale_(self.optimizer)
+        if self.clip is not None and self.clip > 0:
+            clip_grad_norm(self.model.parameters(), self.clip)
+        if self.scaler is not None:
+            self.scaler.step(self.optimizer)
+            self.scaler.update()
+        else:
+            self.optimizer.step()
+        if self.lr_scheduler is not None:
+            self.lr_scheduler.step()
+        self.optimizer.zero_grad(set_to_none=True)
+        self.steps += 1
+        return total / n if n > 1 else total
+
+    @torch.no_grad()
+    def evaluate(self, batch):
+        self.model.eval()
+        batch = self.to_device(batch)
+        with self._autocast():
+            out, targets = self.forward_fn(self.model, batch)
+            loss = self.criterion(out, targets)
+        return out, targets, loss

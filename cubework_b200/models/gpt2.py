@@ -1,0 +1,124 @@
+"""GPT-2 family on the parallel layers.
+
+Parity: benchmark/gpt2/gpt2.py:16-373 — vocab-parallel word embedding + position embedding, pre-LN
+blocks (optional post-LN), packed per-head QKV, GELU MLP, LM head tied to the word-embedding table,
+shifted causal-LM loss, presets ``gpt2_small ... gpt2_40b`` (``gpt2_xl``: hidden 1600, 64 heads,
+48 layers).  The attention is a fused causal kernel instead of materialised ``[b, heads, T, T]``
+scores with a ``tril`` mask rebuilt every call (gpt2.py:75-91).
+"""
+import torch
+import torch.nn as nn
+
+from .. import module as cube_nn
+from .common import MLP, SelfAttention, key_bias_from_mask, maybe_checkpoint, normal_init
+
+
+class GPT2Embedding(nn.Module):
+
+    def __init__(self, embedding_size, vocab_size, max_position_embeddings, padding_idx=None, dropout=0.0,
+                 init_std=None):
+        super().__init__()
+        kw = {} if init_std is None else dict(weight_initializer=normal_init(init_std))
+        self.word_embeddings = cube_nn.Embedding(vocab_size, embedding_size, vocab_parallel=True,
+                                                 padding_idx=padding_idx, **kw)
+        self.position_embeddings = cube_nn.Embedding(max_position_embeddings, embedding_size, **kw)
+        self.dropout = cube_nn.Dropout(dropout)
+
+    def forward(self, input_ids):
+        t = input_ids.size(1)
+        pos = torch.arange(t, dtype=torch.long, device=input_ids.device).unsqueeze(0)
+        return self.dropout(self.word_embeddings(input_ids) + self.position_embeddings(pos))
+
+
+class GPT2Block(nn.Module):
+
+    def __init__(self, hidden_size, num_heads, intermediate_size, attention_dropout=0.0, dropout=0.0,
+                 layernorm_epsilon=1e-5, bias=True, apply_post_layernorm=False, checkpoint=False, init_std=None,
+                 out_std=None):
+        super().__init__()
+        self.checkpoint, self.apply_post_layernorm = checkpoint, apply_post_layernorm
+        wi = None if init_std is None else dict(weight_initializer=normal_init(init_std))
+        wo = None if out_std is None else dict(weight_initializer=normal_init(out_std))
+        self.norm1 = cube_nn.LayerNorm(hidden_size, eps=layernorm_epsilon)
+        self.attn = SelfAttention(hidden_size, num_heads, attention_dropout, dropout, bias=bias, causal=True,
+                                  qkv_kw=wi, out_kw=wo)
+        self.norm2 = cube_nn.LayerNorm(hidden_size, eps=layernorm_epsilon)
+        self.mlp = MLP(hidden_size, intermediate_size, "gelu", dropout, bias=bias, kw1=wi, kw2=wo)
+
+    def _forward(self, x, key_bias=None):
+        h = self.norm1(x)
+        x = (h if self.apply_post_layernorm else x) + self.attn(h, key_bias)
+        h = self.norm2(x)
+        return (h if self.apply_post_layernorm else x) + self.mlp(h)
+
+    def forward(self, x, key_bias=None):
+        return maybe_checkpoint(self._forward, self.checkpoint and self.training, x, key_bias)
+
+
+class GPT2LMLoss(nn.Module):
+    """Next-token loss: logits at position t against the label at t+1."""
+
+    def __init__(self):
+        super().__init__()
+        self.loss = cube_nn.CrossEntropyLoss()
+
+    def forward(self, logits, labels):
+        shift_logits = logits[..., :-1, :].contiguous()
+        shift_labels = labels[..., 1:].contiguous()
+        return self.loss(shift_logits.view(-1, shift_logits.size(-1)), shift_labels.view(-1))
+
+
+class GPT2(nn.Module):
+
+    def __init__(self, vocab_size=50304, max_position_embeddings=1024, hidden_size=768, num_heads=12,
+                 intermediate_size=3072, depth=12, dropout=0.1, embedding_dropout=0.1, attention_dropout=0.0,
+                 layernorm_epsilon=1e-5, padding_idx=None, bias=True, apply_post_layernorm=False, checkpoint=False,
+                 init_std=None):
+        super().__init__()
+        out_std = None if init_std is None else init_std
+        self.embed = GPT2Embedding(hidden_size, vocab_size, max_position_embeddings, padding_idx, embedding_dropout,
+                                   init_std)
+        self.blocks = nn.ModuleList([
+            GPT2Block(hidden_size, num_heads, intermediate_size, attention_dropout, dropout, layernorm_epsilon, bias,
+                      apply_post_layernorm, checkpoint, init_std, out_std) for _ in range(depth)
+        ])
+        self.norm = cube_nn.LayerNorm(hidden_size, eps=layernorm_epsilon)
+        self.head = cube_nn.Classifier(hidden_size, vocab_size, weight=self.embed.word_embeddings.weight, bias=False)
+
+    def forward(self, input_ids, attention_mask=None):
+        x = self.embed(input_ids)
+        key_bias = key_bias_from_mask(attention_mask)
+        for block in self.blocks:
+            x = block(x, key_bias)
+        return self.head(self.norm(x))
+
+
+_PRESETS = {
+    "gpt2_small": dict(hidden_size=768, intermediate_size=3072, depth=12, num_heads=16),
+    "gpt2_medium": dict(hidden_size=1024, intermediate_size=4096, depth=24, num_heads=16),
+    "gpt2_large": dict(hidden_size=1280, intermediate_size=5120, depth=36, num_heads=20),
+    "gpt2_xl": dict(hidden_size=1600, intermediate_size=6400, depth=48, num_heads=64),
+    "gpt2_5b": dict(hidden_size=2880, intermediate_size=11520, depth=50, num_heads=64),
+    "gpt2_10b": dict(hidden_size=4096, intermediate_size=16384, depth=50, num_heads=64),
+    "gpt2_20b": dict(hidden_size=5760, intermediate_size=23040, depth=50, num_heads=64),
+    "gpt2_40b": dict(hidden_size=8192, intermediate_size=32768, depth=50, num_heads=64),
+    "gpt2_tiny": dict(hidden_size=128, intermediate_size=512, depth=2, num_heads=4, vocab_size=1024),
+}
+
+
+def build_model(name, max_position_embeddings=1024, checkpoint=False, **overrides):
+    cfg = dict(_PRESETS[name])
+    cfg.update(max_position_embeddings=max_position_embeddings, checkpoint=checkpoint)
+    cfg.update(overrides)
+    return GPT2(**cfg)
+
+
+def _preset(name):
+    def f(max_position_embeddings=1024, checkpoint=False, **kw):
+        return build_model(name, max_position_embeddings, checkpoint, **kw)
+    f.__name__ = name
+    return f
+
+
+for _n in _PRESETS:
+    globals()[_n] = _preset(_n)

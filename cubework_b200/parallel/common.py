@@ -17,8 +17,23 @@ import torch
 from ..global_vars import NUM_PARTITIONS, env
 
 
-def set_tensor_parallel_attribute_by_partition(param, num_partitions):
+SHARD_SPEC = "SHARD_SPEC"
+
+
+def set_tensor_parallel_attribute_by_partition(param, num_partitions, spec=None):
+    """Stamp the number of distinct shards and, optionally, how the shard was cut.
+
+    ``spec`` is a list of ``(dim, group name)`` in nesting order: the logical tensor is chunked along
+    ``dim`` over the named group, then the result along the next entry, and so on.  Parameters without
+    a spec are replicated.  The checkpoint code gathers / reshards from this record alone.
+    """
     setattr(param, NUM_PARTITIONS, num_partitions)
+    if spec is not None:
+        setattr(param, SHARD_SPEC, [(int(d), m if isinstance(m, str) else m.name) for d, m in spec])
+
+
+def get_shard_spec(param):
+    return list(getattr(param, SHARD_SPEC, []))
 
 
 def get_tensor_parallel_mode():

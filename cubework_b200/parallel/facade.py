@@ -35,14 +35,25 @@ _W_INIT = init.kaiming_uniform_(a=math.sqrt(5))
 _B_INIT = init.xavier_uniform_(a=1, scale=1)
 
 _parallel_layernorm = {"1d": LayerNorm1D, "2d": LayerNorm2D, "3d": LayerNorm3D}
-_parallel_linear = {"1d": Linear1D, "2d": Linear2D, "3d": Linear3D}
+
+
+def _linear_1d(*args, **kwargs):
+    """Column or row layer directly (no ``Linear1D`` wrapper), so parameter names are the same in every mode."""
+    return Linear1D(*args, **kwargs).linear
+
+
+def _patch_embedding_1d(*args, **kwargs):
+    return PatchEmbedding1D(*args, **kwargs).embed
+
+
+_parallel_linear = {"1d": _linear_1d, "2d": Linear2D, "3d": Linear3D}
 _parallel_classifier = {None: ClassifierSTD, "1d": Classifier1D, "2d": Classifier2D, "3d": Classifier3D}
 _vocab_parallel_classifier = {"1d": VocabParallelClassifier1D, "2d": VocabParallelClassifier2D,
                               "3d": VocabParallelClassifier3D}
 _parallel_embedding = {"1d": Embedding1D, "2d": Embedding2D, "3d": Embedding3D}
 _vocab_parallel_embedding = {"1d": VocabParallelEmbedding1D, "2d": VocabParallelEmbedding2D,
                              "3d": VocabParallelEmbedding3D}
-_parallel_patchembedding = {None: PatchEmbeddingSTD, "1d": PatchEmbedding1D, "2d": PatchEmbedding2D,
+_parallel_patchembedding = {None: PatchEmbeddingSTD, "1d": _patch_embedding_1d, "2d": PatchEmbedding2D,
                             "3d": PatchEmbedding3D}
 _parallel_split_batch = {"2d": split_batch_2d, "3d": split_batch_3d}
 

@@ -58,9 +58,9 @@ class Linear1D_Col(nn.Module):
             weight_initializer(self.weight, fan_in=in_features, fan_out=out_features)
             if bias:
                 bias_initializer(self.bias, fan_in=in_features)
-        _stamp(self.weight, n)
+        _stamp(self.weight, n, [(0, "PARALLEL_1D")])
         if bias:
-            _stamp(self.bias, n)
+            _stamp(self.bias, n, [(0, "PARALLEL_1D")])
         set_parallel_input(True)
 
     def forward(self, x):
@@ -92,7 +92,7 @@ class Linear1D_Row(nn.Module):
         if bias:
             with torch.no_grad():
                 broadcast(self.bias.data, pm.PARALLEL_1D.rank_by_idx(0), pm.PARALLEL_1D)
-        _stamp(self.weight, n)
+        _stamp(self.weight, n, [(-1, "PARALLEL_1D")])
         set_parallel_input(False)
 
     def forward(self, x):
@@ -163,7 +163,7 @@ class Classifier1D(nn.Module):
             with torch.no_grad():
                 broadcast(self.bias.data, pm.PARALLEL_1D.rank_by_idx(0), pm.PARALLEL_1D)
         if self.has_weight:
-            _stamp(self.weight, pm.TENSOR.world_size)
+            _stamp(self.weight, pm.TENSOR.world_size, [(-1, "PARALLEL_1D")])
         set_parallel_input(False)
         env.vocab_parallel = False
 
@@ -193,9 +193,9 @@ class VocabParallelClassifier1D(nn.Module):
             if bias:
                 bias_initializer(self.bias, fan_in=in_features)
         if self.has_weight:
-            _stamp(self.weight, n)
+            _stamp(self.weight, n, [(0, "PARALLEL_1D")])
         if bias:
-            _stamp(self.bias, n)
+            _stamp(self.bias, n, [(0, "PARALLEL_1D")])
         set_parallel_input(False)
         env.vocab_parallel = True
 
@@ -217,7 +217,7 @@ class Embedding1D(nn.Module):
             if padding_idx is not None:
                 with torch.no_grad():
                     self.weight[padding_idx].fill_(0)
-        _stamp(self.weight, n)
+        _stamp(self.weight, n, [(-1, "PARALLEL_1D")])
         set_parallel_input(False)
 
     def forward(self, ids):
@@ -242,7 +242,7 @@ class VocabParallelEmbedding1D(nn.Module):
             if padding_idx is not None and self.vocab_start_index <= padding_idx < self.vocab_end_index:
                 with torch.no_grad():
                     self.weight[padding_idx - self.vocab_start_index].fill_(0)
-        _stamp(self.weight, n)
+        _stamp(self.weight, n, [(0, "PARALLEL_1D")])
         set_parallel_input(False)
         env.vocab_parallel = True
 

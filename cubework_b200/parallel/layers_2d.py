@@ -66,9 +66,10 @@ class Linear2D(_Grid2D):
             weight_initializer(self.weight, fan_in=in_features, fan_out=out_features)
             if bias:
                 bias_initializer(self.bias, fan_in=in_features)
-        _stamp(self.weight, q * q)
+        _stamp(self.weight, q * q, [(0, COL), (-1, ROW)])
+        self.weight.STORED_IN_OUT = True   # [in, out]; checkpoints canonicalise to [out, in]
         if bias:
-            _stamp(self.bias, q * q)
+            _stamp(self.bias, q * q, [(-1, ROW), (-1, COL)])
 
     def forward(self, x):
         out_shape = x.shape[:-1] + (self.hidden_size_per_partition, )
@@ -89,8 +90,8 @@ class LayerNorm2D(_Grid2D):
         self.partitioned_partition = self._div(normalized_shape, q * q, "normalized_shape")
         self.weight = Parameter(torch.ones(self.partitioned_partition))
         self.bias = Parameter(torch.zeros(self.partitioned_partition))
-        _stamp(self.weight, q * q)
-        _stamp(self.bias, q * q)
+        _stamp(self.weight, q * q, [(-1, ROW), (-1, COL)])
+        _stamp(self.bias, q * q, [(-1, ROW), (-1, COL)])
 
     def forward(self, x):
         gamma = all_gather_tensor_2d(self.weight, -1, pm.PARALLEL_2D_COL)
@@ -121,8 +122,10 @@ class PatchEmbedding2D(_Grid2D):
             weight_initializer(self.weight, fan_in=fan_in, fan_out=embed_size)
             bias_initializer(self.bias, fan_in=fan_in)
             position_embed_initializer(self.pos_embed)
-        for p in (self.weight, self.bias, self.cls_token, self.pos_embed):
-            _stamp(p, q * q)
+        for p in (self.weight, self.bias):
+            _stamp(p, q * q, [(0, ROW), (0, COL)])
+        for p in (self.cls_token, self.pos_embed):
+            _stamp(p, q * q, [(-1, ROW), (-1, COL)])
 
     def forward(self, images):
         images = split_batch_2d(images)
@@ -150,7 +153,7 @@ class Embedding2D(_Grid2D):
             if padding_idx is not None:
                 with torch.no_grad():
                     self.weight[padding_idx].fill_(0)
-        _stamp(self.weight, q * q)
+        _stamp(self.weight, q * q, [(-1, ROW), (-1, COL)])
 
     def forward(self, ids):
         ids = split_batch_2d(ids)
@@ -175,7 +178,7 @@ class VocabParallelEmbedding2D(_Grid2D):
             if padding_idx is not None and self.vocab_start_index <= padding_idx < self.vocab_end_index:
                 with torch.no_grad():
                     self.weight[padding_idx - self.vocab_start_index].fill_(0)
-        _stamp(self.weight, q * q)
+        _stamp(self.weight, q * q, [(-1, ROW), (0, COL)])
         env.vocab_parallel = True
 
     def forward(self, ids):
@@ -205,7 +208,7 @@ class Classifier2D(_Grid2D):
                 broadcast(self.bias.data, pm.PARALLEL_2D_COL.rank_by_idx(0), pm.PARALLEL_2D_COL)
                 broadcast(self.bias.data, pm.PARALLEL_2D_ROW.rank_by_idx(0), pm.PARALLEL_2D_ROW)
         if self.has_weight:
-            _stamp(self.weight, q * q)
+            _stamp(self.weight, q * q, [(-1, ROW), (-1, COL)])
 
     def forward(self, x):
         out_shape = x.shape[:-1] + (self.num_classes, )
@@ -232,9 +235,9 @@ class VocabParallelClassifier2D(_Grid2D):
             if bias:
                 bias_initializer(self.bias, fan_in=in_features)
         if self.has_weight:
-            _stamp(self.weight, q * q)
+            _stamp(self.weight, q * q, [(0, COL), (-1, ROW)])
         if bias:
-            _stamp(self.bias, q * q)
+            _stamp(self.bias, q * q, [(0, ROW), (0, COL)])
         env.vocab_parallel = True
 
     def forward(self, x):

@@ -69,8 +69,8 @@ class LayerNorm3D(_Cube):
         self.normalized_shape_per_partition = _div(normalized_shape, d, "normalized_shape")
         self.weight = Parameter(torch.ones(self.normalized_shape_per_partition))
         self.bias = Parameter(torch.zeros(self.normalized_shape_per_partition))
-        _stamp(self.weight, d)
-        _stamp(self.bias, d)
+        _stamp(self.weight, d, [(0, self.output_parallel_mode)])
+        _stamp(self.bias, d, [(0, self.output_parallel_mode)])
 
     def forward(self, x):
         return layernorm_3d(x, self.weight, self.bias, self.normalized_shape, self.variance_epsilon,
@@ -98,9 +98,11 @@ class Linear3D(_Cube):
             with torch.no_grad():
                 m = self.output_x_weight_parallel_mode
                 broadcast(self.bias.data, m.rank_by_idx(0), m)
-        _stamp(self.weight, d**3)
+        _stamp(self.weight, d**3, [(0, self.output_parallel_mode), (-1, self.input_parallel_mode),
+                                   (-1, self.weight_parallel_mode)])
+        self.weight.STORED_IN_OUT = True   # [in, out]; checkpoints canonicalise to [out, in]
         if bias:
-            _stamp(self.bias, d)
+            _stamp(self.bias, d, [(0, self.input_parallel_mode)])
         swap_in_out_group()
 
     def forward(self, x):
@@ -132,7 +134,7 @@ class Classifier3D(_Cube):
             if bias:
                 broadcast(self.bias.data, pm.TENSOR.rank_by_idx(0), pm.TENSOR)
         if self.has_weight:
-            _stamp(self.weight, d)
+            _stamp(self.weight, d, [(-1, self.output_parallel_mode)])
 
     def forward(self, x):
         return classifier_3d(x, self.weight, self.bias, self.input_parallel_mode, self.weight_parallel_mode,
@@ -164,9 +166,10 @@ class VocabParallelClassifier3D(_Cube):
                 m = self.output_x_weight_parallel_mode
                 broadcast(self.bias.data, m.rank_by_idx(0), m)
         if self.has_weight:
-            _stamp(self.weight, d**3)
+            _stamp(self.weight, d**3, [(0, self.input_parallel_mode), (0, self.weight_parallel_mode),
+                                       (-1, self.output_parallel_mode)])
         if bias:
-            _stamp(self.bias, d)
+            _stamp(self.bias, d, [(0, self.input_parallel_mode)])
         swap_in_out_group()
         env.vocab_parallel = True
 
@@ -198,8 +201,10 @@ class PatchEmbedding3D(_Cube):
             position_embed_initializer(self.pos_embed)
         params = (self.weight, self.bias, self.cls_token, self.pos_embed)
         self._replicate(params, self.input_x_weight_parallel_mode)
-        for p in params:
-            _stamp(p, d)
+        for p in (self.weight, self.bias):
+            _stamp(p, d, [(0, self.output_parallel_mode)])
+        for p in (self.cls_token, self.pos_embed):
+            _stamp(p, d, [(-1, self.output_parallel_mode)])
 
     def forward(self, images):
         images = split_batch_3d(images, input_parallel_mode=self.input_parallel_mode,
@@ -222,7 +227,7 @@ class Embedding3D(_Cube):
                 with torch.no_grad():
                     self.weight[padding_idx].fill_(0)
         self._replicate((self.weight, ), self.input_x_weight_parallel_mode)
-        _stamp(self.weight, d)
+        _stamp(self.weight, d, [(-1, self.output_parallel_mode)])
 
     def forward(self, ids):
         ids = split_batch_3d(ids, input_parallel_mode=self.input_parallel_mode,
@@ -250,7 +255,8 @@ class VocabParallelEmbedding3D(_Cube):
             if padding_idx is not None and own_start <= padding_idx < own_start + self.num_embeddings_per_partition:
                 with torch.no_grad():
                     self.weight[padding_idx - own_start].fill_(0)
-        _stamp(self.weight, d**3)
+        _stamp(self.weight, d**3, [(0, self.input_parallel_mode), (0, self.weight_parallel_mode),
+                                   (-1, self.output_parallel_mode)])
         env.vocab_parallel = True
 
     def forward(self, ids):

@@ -9,3 +9,5 @@ __all__ = [
     "SyntheticLoader", "get_logger", "init_logger", "write_logger_to_file", "CommProfiler", "MemoryTracker",
     "calc_model_size", "calc_tflops"
 ]
+
+from . import checkpoint  # noqa: E402  (after the names above: it imports the parallel package)
