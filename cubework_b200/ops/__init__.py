@@ -277,15 +277,20 @@ class _AttentionFn(torch.autograd.Function):
     @staticmethod
     def forward(ctx, qkv, causal, key_bias, scale):
         out, lse = ext.attention_fwd(qkv, causal, key_bias, scale)
-        ctx.save_for_backward(qkv, out, lse, key_bias if key_bias is not None else qkv.new_empty(0))
+        if torch.is_tensor(lse):
+            ctx.save_for_backward(qkv, out, lse, key_bias if key_bias is not None else qkv.new_empty(0))
+            ctx.aux = None
+        else:   # interim library path: `lse` carries its own graph
+            ctx.save_for_backward(qkv, out, qkv.new_empty(0), key_bias if key_bias is not None else qkv.new_empty(0))
+            ctx.aux = lse
         ctx.causal, ctx.scale, ctx.has_bias = causal, scale, key_bias is not None
         return out
 
     @staticmethod
     def backward(ctx, dout):
         qkv, out, lse, kb = ctx.saved_tensors
-        dqkv = ext.attention_bwd(dout.contiguous(), qkv, out, lse, ctx.causal, kb if ctx.has_bias else None,
-                                 ctx.scale)
+        dqkv = ext.attention_bwd(dout.contiguous(), qkv, out, lse if ctx.aux is None else ctx.aux, ctx.causal,
+                                 kb if ctx.has_bias else None, ctx.scale)
         return dqkv, None, None, None
 
 
