@@ -41,6 +41,7 @@ std::vector<torch::Tensor> attention_fwd(torch::Tensor qkv, bool causal, c10::op
                                          double scale, int64_t status_ptr);
 torch::Tensor attention_bwd(torch::Tensor dout, torch::Tensor qkv, torch::Tensor out, torch::Tensor lse, bool causal,
                             c10::optional<torch::Tensor> key_bias, double scale, int64_t status_ptr);
+bool attention_ready();
 // comm.cu
 void register_comm(pybind11::module& m);
 
@@ -138,5 +139,6 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("multi_scale", &cw::multi_scale);
   m.def("attention_fwd", &cw::attention_fwd);
   m.def("attention_bwd", &cw::attention_bwd);
+  m.def("attention_ready", &cw::attention_ready);
   cw::register_comm(m);
 }

@@ -44,7 +44,35 @@ static torch::Tensor as_tensor(int64_t ptr, std::vector<int64_t> shape, torch::S
   return torch::from_blob(reinterpret_cast<void*>(ptr), shape, opts);
 }
 
+// One thread waits (bounded by `limit_ns`) for *flag >= epoch and records the outcome: 0 = arrived, code 5 = gave up.
+// Used by the failure-detection tests: a wait whose partner never writes must end with a status, not a hang.
+__global__ void probe_wait_kernel(const int* flag, int epoch, unsigned long long limit_ns, int* result) {
+  const unsigned long long t0 = globaltimer_ns();
+  int outcome = kErrPeerFlagTimeout;
+  for (unsigned spin = 0;; ++spin) {
+    int v;
+    asm volatile("ld.acquire.sys.global.b32 %0, [%1];" : "=r"(v) : "l"(flag) : "memory");
+    if (v >= epoch) { outcome = kOk; break; }
+    if ((spin & 63u) == 0) {
+      __nanosleep(200);
+      if (globaltimer_ns() - t0 > limit_ns) break;
+    }
+  }
+  result[0] = outcome;
+  result[1] = static_cast<int>((globaltimer_ns() - t0) / 1000000ull);
+}
+
+static torch::Tensor probe_wait(torch::Tensor flag, int64_t epoch, double limit_ms) {
+  TORCH_CHECK(flag.is_cuda() && flag.scalar_type() == torch::kInt32 && flag.numel() >= 1);
+  auto result = torch::zeros({2}, flag.options());
+  probe_wait_kernel<<<1, 1, 0, at::cuda::getCurrentCUDAStream()>>>(
+      flag.data_ptr<int>(), static_cast<int>(epoch), static_cast<unsigned long long>(limit_ms * 1e6), result.data_ptr<int>());
+  C10_CUDA_KERNEL_LAUNCH_CHECK();
+  return result;
+}
+
 void register_comm(py::module& m) {
+  m.def("probe_wait", &probe_wait);
   m.def("ipc_alloc", &ipc_alloc);
   m.def("ipc_open", &ipc_open);
   m.def("ipc_close", &ipc_close);

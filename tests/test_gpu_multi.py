@@ -1,0 +1,150 @@
+"""Multi-GPU checks (2 ranks, NCCL): the fused GEMM + all-reduce kernel over peer memory, the 1D layers in
+bf16 against an unsharded oracle, one tiny GPT-2 step, and the bounded device-side wait.
+
+The ranks run as child processes, one per GPU.  NVLS is switched off for NCCL in these tests and the fused
+kernels use plain peer loads / stores.
+"""
+import os
+
+import pytest
+import torch
+
+from dist_utils import run_dist
+
+pytestmark = pytest.mark.gpu
+
+
+def _need(n):
+    if torch.cuda.device_count() < n:
+        pytest.skip(f"needs {n} GPUs")
+
+
+def _rel(a, b):
+    a, b = a.float(), b.float()
+    return ((a - b).norm() / (b.norm() + 1e-12)).item()
+
+
+def _check_fused_all_reduce():
+    import torch.distributed as dist
+
+    from cubework_b200.distributed import ParallelManager as pm
+    from cubework_b200.ops import ext
+    from cubework_b200.parallel import fused, symm
+    assert symm.available()
+    mode = pm.PARALLEL_1D
+    n, r = mode.world_size, mode.local_rank
+    dev = torch.device("cuda", torch.cuda.current_device())
+    torch.manual_seed(0)
+    for (M, N, K, ta, tb, with_bias) in [(512, 512, 256, False, True, True), (1000, 1608, 328, False, False, False),
+                                         (4096, 1600, 800, False, True, True), (384, 264, 72, False, True, False)]:
+        a_full = torch.randn(M, K * n, device=dev).bfloat16()
+        b_full = (torch.randn(N, K * n, device=dev) if tb else torch.randn(K * n, N, device=dev)).bfloat16()
+        bias = torch.randn(N, device=dev) if with_bias else None
+        for t in (a_full, b_full) + ((bias, ) if with_bias else ()):
+            dist.broadcast(t, src=0)
+        a = a_full[:, r * K:(r + 1) * K].contiguous()
+        b = (b_full[:, r * K:(r + 1) * K] if tb else b_full[r * K:(r + 1) * K]).contiguous()
+        ref = a_full.float() @ (b_full.float().t() if tb else b_full.float())
+        if with_bias:
+            ref = ref + bias
+        for rep in range(3):   # the workspace and its epochs are reused call after call
+            out = fused.gemm_all_reduce(a, b, ta, tb, mode, bias=bias)
+            torch.cuda.synchronize()
+            ext.check_status()
+            assert _rel(out, ref) < 8e-3, (M, N, K, rep, _rel(out, ref))
+        gathered = [torch.empty_like(out) for _ in range(n)]
+        dist.all_gather(gathered, out)
+        assert all(torch.equal(g, gathered[0]) for g in gathered), "ranks disagree on the reduced result"
+
+
+def _check_layers_bf16():
+    import torch.distributed as dist
+    import torch.nn.functional as F
+
+    import cubework_b200.module as nn_
+    from cubework_b200.distributed import ParallelManager as pm
+    from cubework_b200.ops import ext
+    from cubework_b200.parallel.ops_1d import set_parallel_input
+    n, r = pm.PARALLEL_1D.world_size, pm.PARALLEL_1D.local_rank
+    dev = torch.device("cuda", torch.cuda.current_device())
+    torch.manual_seed(1)
+    B, S, H = 4, 128, 512
+    set_parallel_input(False)
+    col = nn_.Linear(H, 4 * H, activation="gelu").to(dev)
+    row = nn_.Linear(4 * H, H).to(dev)
+    W1, b1 = torch.randn(4 * H, H, device=dev) * 0.05, torch.randn(4 * H, device=dev) * 0.1
+    W2, b2 = torch.randn(H, 4 * H, device=dev) * 0.05, torch.randn(H, device=dev) * 0.1
+    x0 = torch.randn(B, S, H, device=dev)
+    g0 = torch.randn(B, S, H, device=dev)
+    for t in (W1, b1, W2, b2, x0, g0):
+        dist.broadcast(t, src=0)
+    with torch.no_grad():
+        col.weight.copy_(W1.chunk(n, 0)[r]), col.bias.copy_(b1.chunk(n, 0)[r])
+        row.weight.copy_(W2.chunk(n, 1)[r]), row.bias.copy_(b2)
+    x = x0.clone().requires_grad_(True)
+    with torch.autocast("cuda", dtype=torch.bfloat16):
+        y = row(col(x))
+    y.backward(g0.to(y.dtype))
+    torch.cuda.synchronize()
+    ext.check_status()
+    xr = x0.clone().requires_grad_(True)
+    W1r, b1r, W2r, b2r = (t.clone().requires_grad_(True) for t in (W1, b1, W2, b2))
+    yr = F.linear(F.gelu(F.linear(xr, W1r, b1r)), W2r, b2r)
+    yr.backward(g0)
+    assert _rel(y, yr) < 2e-2
+    assert _rel(x.grad, xr.grad) < 2e-2
+    assert _rel(col.weight.grad, W1r.grad.chunk(n, 0)[r]) < 2e-2
+    assert _rel(row.weight.grad, W2r.grad.chunk(n, 1)[r]) < 2e-2
+    assert _rel(row.bias.grad, b2r.grad) < 2e-2 and _rel(col.bias.grad, b1r.grad.chunk(n, 0)[r]) < 2e-2
+
+
+def _check_gpt2_step():
+    from cubework_b200.engine import Trainer
+    from cubework_b200.models import gpt2
+    from cubework_b200.ops import ext
+    from cubework_b200.optim import FusedAdamW
+    dev = torch.device("cuda", torch.cuda.current_device())
+    torch.manual_seed(0)
+    model = gpt2.GPT2(vocab_size=2048, max_position_embeddings=128, hidden_size=256, num_heads=8,
+                      intermediate_size=1024, depth=2, dropout=0.0, embedding_dropout=0.0, init_std=0.02).to(dev)
+    tr = Trainer(model, gpt2.GPT2LMLoss(), FusedAdamW(model.parameters(), lr=1e-3), amp_dtype=torch.bfloat16, clip=1.0)
+    ids = torch.randint(0, 2048, (4, 128), generator=torch.Generator().manual_seed(3))
+    batch = dict(input_ids=ids, attention_mask=torch.ones(4, 128), labels=ids)
+    losses = [tr.step(batch).item() for _ in range(3)]
+    torch.cuda.synchronize()
+    ext.check_status()
+    assert abs(losses[0] - 7.62) < 0.2 and losses[2] < losses[0], losses
+
+
+def _multi(fn, n=2):
+    _need(n)
+    os.environ["NCCL_NVLS_ENABLE"] = "0"
+    run_dist(fn, n, tp="1d", tp_size=n, backend="nccl", use_cuda=True)
+
+
+def test_fused_gemm_all_reduce_two_ranks():
+    _multi(_check_fused_all_reduce)
+
+
+def test_1d_layers_bf16_two_ranks():
+    _multi(_check_layers_bf16)
+
+
+def test_gpt2_step_two_ranks():
+    _multi(_check_gpt2_step)
+
+
+def test_bounded_wait_times_out_and_context_survives():
+    """A flag that nothing sets: the wait must give up after its limit, report it, and leave the GPU usable."""
+    from cubework_b200.ops import ext
+    m = ext.require()
+    flag = torch.zeros(1, dtype=torch.int32, device="cuda")
+    res = m.probe_wait(flag, 1, 50.0)           # 50 ms limit
+    torch.cuda.synchronize()
+    code, waited_ms = res.tolist()
+    assert code == 5 and 40 <= waited_ms <= 2000, (code, waited_ms)
+    flag.fill_(3)
+    res = m.probe_wait(flag, 2, 50.0)
+    assert res.tolist()[0] == 0
+    x = torch.randn(256, 256, device="cuda")     # the context still works
+    assert torch.isfinite((x @ x).sum()).item()
