@@ -28,7 +28,30 @@ def so_path():
     return os.path.join(HERE, NAME + ".so")
 
 
+NOALLOC_SRC = os.path.join(CSRC, "noalloc", "noalloc_layer_norm_bwd.cu")
+
+
+def noalloc_so_path():
+    return os.path.join(HERE, "libcubework_noalloc.so")
+
+
+def build_noalloc(verbose=False):
+    """The allocation-free entry point is a plain CUDA library (no torch, no Python): one nvcc call."""
+    import subprocess
+    out = noalloc_so_path()
+    if os.path.exists(out) and os.path.getmtime(out) >= max(os.path.getmtime(NOALLOC_SRC),
+                                                            os.path.getmtime(NOALLOC_SRC[:-3] + ".h")):
+        return out
+    cmd = ["nvcc", "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17", "-shared",
+           "-Xcompiler", "-fPIC", "-o", out, NOALLOC_SRC]
+    if verbose:
+        cmd[1:1] = ["-Xptxas", "-v"]
+    subprocess.run(cmd, check=True)
+    return out
+
+
 def build(verbose=False):
+    build_noalloc(verbose)
     os.environ.setdefault("TORCH_CUDA_ARCH_LIST", "10.0a")
     os.environ.setdefault("MAX_JOBS", str(min(16, os.cpu_count() or 4)))
     from torch.utils import cpp_extension
