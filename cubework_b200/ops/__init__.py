@@ -276,20 +276,18 @@ class _AttentionFn(torch.autograd.Function):
 
     @staticmethod
     def forward(ctx, qkv, causal, key_bias, scale):
-        out, lse = ext.attention_fwd(qkv, causal, key_bias, scale)
-        if torch.is_tensor(lse):
-            ctx.save_for_backward(qkv, out, lse, key_bias if key_bias is not None else qkv.new_empty(0))
-            ctx.aux = None
-        else:   # interim library path: `lse` carries its own graph
-            ctx.save_for_backward(qkv, out, qkv.new_empty(0), key_bias if key_bias is not None else qkv.new_empty(0))
-            ctx.aux = lse
-        ctx.causal, ctx.scale, ctx.has_bias = causal, scale, key_bias is not None
+        out, (lse, packed) = ext.attention_fwd(qkv, causal, key_bias, scale)
+        empty = qkv.new_empty(0)
+        # `packed` is the padded, TMA-aligned copy of QKV that odd head dims need; keep it for the backward
+        ctx.save_for_backward(qkv, out, lse, key_bias if key_bias is not None else empty,
+                              packed if packed is not None else empty)
+        ctx.causal, ctx.scale, ctx.has_bias, ctx.has_packed = causal, scale, key_bias is not None, packed is not None
         return out
 
     @staticmethod
     def backward(ctx, dout):
-        qkv, out, lse, kb = ctx.saved_tensors
-        dqkv = ext.attention_bwd(dout.contiguous(), qkv, out, lse if ctx.aux is None else ctx.aux, ctx.causal,
+        qkv, out, lse, kb, packed = ctx.saved_tensors
+        dqkv = ext.attention_bwd(dout.contiguous(), qkv, out, (lse, packed if ctx.has_packed else None), ctx.causal,
                                  kb if ctx.has_bias else None, ctx.scale)
         return dqkv, None, None, None
 

@@ -40,7 +40,8 @@ void multi_scale(std::vector<torch::Tensor> grads, torch::Tensor coef);
 std::vector<torch::Tensor> attention_fwd(torch::Tensor qkv, bool causal, c10::optional<torch::Tensor> key_bias,
                                          double scale, int64_t status_ptr);
 torch::Tensor attention_bwd(torch::Tensor dout, torch::Tensor qkv, torch::Tensor out, torch::Tensor lse, bool causal,
-                            c10::optional<torch::Tensor> key_bias, double scale, int64_t status_ptr);
+                            c10::optional<torch::Tensor> key_bias, double scale, int64_t status_ptr,
+                            c10::optional<torch::Tensor> packed);
 bool attention_ready();
 // comm.cu
 void register_comm(pybind11::module& m);

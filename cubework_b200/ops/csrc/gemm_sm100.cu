@@ -45,6 +45,24 @@ CUtensorMap make_tma_2d(const void* ptr, uint64_t rows, uint64_t cols, uint64_t 
   return m;
 }
 
+// 4-D map over 16-bit data [d3][d2][d1][d0] (d0 innermost, strides in bytes for d1..d3), box = 64 x 128 x 1 x 1.
+// Reads past any extent are zero-filled, which is how tiles get their padding.
+CUtensorMap make_tma_4d(const void* ptr, uint64_t d0, uint64_t d1, uint64_t d2, uint64_t d3, uint64_t s1, uint64_t s2,
+                        uint64_t s3) {
+  TORCH_CHECK((reinterpret_cast<uintptr_t>(ptr) & 15) == 0, "TMA operand must be 16-byte aligned");
+  TORCH_CHECK(s1 % 16 == 0 && s2 % 16 == 0 && s3 % 16 == 0, "TMA strides must be multiples of 16 bytes");
+  CUtensorMap m;
+  cuuint64_t dims[4] = {d0, d1, d2, d3};
+  cuuint64_t strides[3] = {s1, s2, s3};
+  cuuint32_t box[4] = {64, 128, 1, 1};
+  cuuint32_t estr[4] = {1, 1, 1, 1};
+  CUresult r = get_encode()(&m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(ptr), dims, strides, box, estr,
+                            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  TORCH_CHECK(r == CUDA_SUCCESS, "cuTensorMapEncodeTiled (4-D) failed with code ", static_cast<int>(r));
+  return m;
+}
+
 template <int BN, bool A_KMAJOR, bool B_KMAJOR, typename InT, bool OUT_F32>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b, GemmParams p) {

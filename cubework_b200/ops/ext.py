@@ -239,32 +239,13 @@ def multi_sgd(params, grads, bufs, shadows, lr, momentum, wd, first, grad_scale)
 
 def attention_fwd(qkv, causal, key_bias, scale):
     m = require()
-    if not has("attention"):
-        _warn_once("attn", "fused attention kernel is not built; using the library attention path")
-        B, T, H, D3 = qkv.shape
-        q, k, v = qkv.permute(0, 2, 1, 3).chunk(3, dim=-1)
-        mask = None
-        if key_bias is not None:
-            mask = key_bias.to(q.dtype)[:, None, None, :].expand(B, 1, T, T)
-            if causal:
-                mask = mask + torch.full((T, T), float("-inf"), device=q.device, dtype=q.dtype).triu(1)
-        with torch.enable_grad():
-            qd, kd, vd = (t.detach().requires_grad_(True) for t in (q, k, v))
-            o = torch.nn.functional.scaled_dot_product_attention(qd, kd, vd, attn_mask=mask,
-                                                                 is_causal=causal and mask is None, scale=scale)
-        out = o.detach().transpose(1, 2).contiguous()
-        return out, (o, qd, kd, vd)
-    _count(1)
-    out, lse = m.attention_fwd(qkv, bool(causal), key_bias, float(scale), m.status_device_ptr())
-    return out, lse
+    out, lse, packed = m.attention_fwd(qkv, bool(causal), key_bias, float(scale), m.status_device_ptr())
+    _count(1 if packed is None else 2)
+    return out, (lse, packed)
 
 
 def attention_bwd(dout, qkv, out, lse, causal, key_bias, scale):
     m = require()
-    if not has("attention"):
-        o, qd, kd, vd = lse
-        B, T, H, dh = dout.shape[0], dout.shape[1], qd.shape[1], qd.shape[-1]
-        gq, gk, gv = torch.autograd.grad(o, (qd, kd, vd), dout.view(B, T, H, dh).transpose(1, 2))
-        return torch.cat([gq, gk, gv], dim=-1).permute(0, 2, 1, 3).contiguous()
-    _count(2)
-    return m.attention_bwd(dout, qkv, out, lse, bool(causal), key_bias, float(scale), m.status_device_ptr())
+    lse, packed = lse
+    _count(3 if packed is None else 4)
+    return m.attention_bwd(dout, qkv, out, lse, bool(causal), key_bias, float(scale), m.status_device_ptr(), packed)
