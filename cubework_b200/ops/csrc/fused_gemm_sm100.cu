@@ -5,15 +5,18 @@
 //   out = sum over ranks( op(A_r) * op(B_r) ) + bias          identical on every rank of the group
 //
 // Grid = G GEMM CTAs + R communication CTAs, all co-resident (one CTA per SM).
-//  * GEMM CTAs: the persistent TMA -> tcgen05 -> TMEM pipeline of gemm_sm100.cu; the epilogue stores each
-//    partial tile (16-bit) straight into the *owner's* staging buffer through its peer pointer (tile t is
-//    owned by rank t mod n) and then publishes an arrival flag there.
-//  * communication CTAs, tile by tile in production order:
+//  * GEMM CTAs: the persistent TMA -> tcgen05 -> TMEM pipeline of gemm_sm100.cu; each epilogue warp converts
+//    its 32 rows of the partial tile to 16-bit in shared memory and sends them with one 16 KB bulk copy
+//    straight into the *owner's* staging buffer through its peer pointer (tile t is owned by rank t mod n),
+//    then publishes an arrival flag there.
+//  * communication CTAs, tile by tile in production order; warp 0 issues, warps 1-5 work:
 //      owner:  wait for the n partials, sum them in fp32 (+ bias), write the result tile to its own output
 //              and to its result buffer, publish a "done" flag to every peer;
-//      others: wait for "done", pull the result tile from the owner's result buffer into their output.
+//      others: warp 0 waits for "done" and bulk-copies the result tile from the owner's result buffer into one
+//              of three shared-memory slots (running up to three tiles ahead); the workers copy it to the output.
 // Flags hold a call epoch that only grows, so nothing is ever reset.  Every wait is bounded and reports to
-// the status word.  All remote accesses are ordinary ld/st through IPC-mapped pointers.
+// the status word.  Remote accesses are bulk copies and ordinary ld/st through IPC-mapped pointers; no TMA
+// tensor map ever covers peer memory.
 //
 // The reference issues a cuBLAS GEMM and then a blocking NCCL all-reduce (cubework/module/parallel_1d/
 // module.py:331-346 -> _utils.py:73-74; backward _utils.py:63-64).
@@ -77,6 +80,32 @@ __device__ __forceinline__ bool wait_flag(const int* flag, int epoch, int* statu
   }
 }
 
+constexpr int kFusedStages = 3;
+constexpr int kSlabBytes = 32 * kFusedBN * 2;                 // one epilogue warp's 32 rows of a tile (16 KB)
+constexpr int kEpiBytes = 4 * kSlabBytes;                      // 64 KB
+constexpr int kPullSlots = 3;
+constexpr int kTileBytes = kTileElems * 2;                     // 64 KB
+constexpr int kFusedSmemBytes = kFusedStages * GemmCfg<kFusedBN>::kStageBytes + kEpiBytes + 256 + 1024;
+static_assert(kPullSlots * kTileBytes + 256 + 1024 <= kFusedSmemBytes, "pull slots must fit the same allocation");
+constexpr int kWorkers = kGemmThreads - 32;                    // communication CTA: warp 0 issues, warps 1-5 work
+
+__device__ __forceinline__ void bulk_store(void* gdst, const void* ssrc, uint32_t bytes) {
+  asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(gdst), "r"(smem_u32(ssrc)), "r"(bytes)
+               : "memory");
+}
+__device__ __forceinline__ void bulk_load(void* sdst, const void* gsrc, uint32_t bytes, uint64_t* bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+                   smem_u32(sdst)),
+               "l"(gsrc), "r"(bytes), "r"(smem_u32(bar))
+               : "memory");
+}
+__device__ __forceinline__ void worker_sync() { asm volatile("bar.sync 1, %0;" ::"n"(kWorkers) : "memory"); }
+
+// Element offset of 16-byte chunk j (0..31) of row r inside a staged 128 x 256 tile.  The chunk position is
+// XOR-ed with the row so the epilogue's row-per-lane shared-memory writes are bank-conflict free; the staged tile
+// is copied verbatim to the owner, whose reducer applies the same mapping when it reads.
+__device__ __forceinline__ int staged_off(int r, int j) { return r * kFusedBN + ((j ^ (r & 31)) << 3); }
+
 template <bool A_KMAJOR, bool B_KMAJOR, typename InT>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_allreduce_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
@@ -85,12 +114,6 @@ gemm_allreduce_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_co
   using Cfg = GemmCfg<BN>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + Cfg::kStages * Cfg::kStageBytes);
-  uint64_t* empty_bar = full_bar + Cfg::kStages;
-  uint64_t* tfull_bar = empty_bar + Cfg::kStages;
-  uint64_t* tempty_bar = tfull_bar + 2;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty_bar + 2);
-  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -102,100 +125,125 @@ gemm_allreduce_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_co
 
   if (is_comm) {
     // =============================================================== communication CTA
-    __shared__ int s_ok;
+    uint8_t* slots = smem;                                            // kPullSlots x 64 KB
+    uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + kPullSlots * kTileBytes);
+    uint64_t* empty_bar = full_bar + kPullSlots;
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(empty_bar + kPullSlots);
+    if (threadIdx.x == 0) {
+      for (int s = 0; s < kPullSlots; ++s) {
+        mbar_init(&full_bar[s], 1);
+        mbar_init(&empty_bar[s], kWorkers / 32);
+      }
+      *abort_flag = 0;
+      fence_barrier_init();
+    }
+    __syncthreads();
     const int c = blockIdx.x - p.num_gemm_ctas;
+    if (warp == 0) {
+      // ---- issuer: runs ahead of the workers, fetching finished tiles of other owners into free slots
+      if (lane == 0) {
+        int slot = 0;
+        uint32_t phase = 0;
+        for (int t = c; t < num_tiles && !*abort_flag; t += p.num_comm_ctas) {
+          const int owner = t % p.n;
+          if (owner == p.me) continue;
+          if (!mbar_wait(&empty_bar[slot], phase ^ 1, abort_flag, p.status, kErrPeerFlagTimeout, t)) break;
+          if (!wait_flag(p.flags[p.me] + t, p.epoch, p.status, t)) { *abort_flag = 1; break; }
+          const uint8_t* src = reinterpret_cast<const uint8_t*>(p.result[owner]) + static_cast<size_t>(t / p.n) * kTileBytes;
+          mbar_expect_tx(&full_bar[slot], kTileBytes);
+#pragma unroll
+          for (int q = 0; q < 4; ++q)
+            bulk_load(slots + slot * kTileBytes + q * (kTileBytes / 4), src + q * (kTileBytes / 4), kTileBytes / 4,
+                      &full_bar[slot]);
+          if (++slot == kPullSlots) { slot = 0; phase ^= 1; }
+        }
+      }
+      return;
+    }
+    // ---- workers
+    const int wid = threadIdx.x - 32;
     InT* out = reinterpret_cast<InT*>(p.out);
+    int slot = 0;
+    uint32_t phase = 0;
     for (int t = c; t < num_tiles; t += p.num_comm_ctas) {
+      if (*abort_flag) break;
       int tile_m, tile_n, kb0, kb1;
       decode_work(t, num_tiles, tiles_m, tiles_n, kb_total, 1, tile_m, tile_n, kb0, kb1);
       const int owner = t % p.n;
       const int li = t / p.n;
       const int rows = min(kBM, p.M - tile_m * kBM);
       const int cols = min(BN, p.N - tile_n * BN);
-      const int vec_per_row = (cols + 7) / 8;               // 16-byte vectors (N is a multiple of 8)
+      const int vec_per_row = cols >> 3;                    // 16-byte vectors (N is a multiple of 8)
       const int total_vec = rows * vec_per_row;
-      if (threadIdx.x == 0) s_ok = 1;
-      __syncthreads();
+      InT* out_tile = out + static_cast<size_t>(tile_m * kBM) * p.N + tile_n * BN;
       if (owner == p.me) {
-        // ---- wait for the n x 4 arrival words of this tile
-        if (warp == 0) {
+        // wait for the n x 4 arrival words of this tile, then sum the n staged partials
+        if (warp == 1) {
           const int nflags = p.n * 4;
-          bool ok = true;
           for (int f = lane; f < nflags; f += 32)
-            ok = wait_flag(p.flags[p.me] + p.done_cap + static_cast<size_t>(li) * nflags + f, p.epoch, p.status, t) && ok;
-          if (!ok) s_ok = 0;
+            if (!wait_flag(p.flags[p.me] + p.done_cap + static_cast<size_t>(li) * nflags + f, p.epoch, p.status, t))
+              *abort_flag = 1;
         }
-        __syncthreads();
-        if (!s_ok) break;
+        worker_sync();
+        if (*abort_flag) break;
         const InT* stage = reinterpret_cast<const InT*>(p.stage[p.me]) + static_cast<size_t>(li) * p.n * kTileElems;
         InT* res = reinterpret_cast<InT*>(p.result[p.me]) + static_cast<size_t>(li) * kTileElems;
-        for (int v = threadIdx.x; v < total_vec; v += kGemmThreads) {
-          const int r = v / vec_per_row, cv = (v - r * vec_per_row) * 8;
+        for (int v = wid; v < total_vec; v += kWorkers) {
+          const int r = v / vec_per_row, j = v - r * vec_per_row;
           float acc[8];
 #pragma unroll
           for (int i = 0; i < 8; ++i) acc[i] = 0.f;
+          const int off = staged_off(r, j);
           for (int src = 0; src < p.n; ++src) {
-            const uint4 raw = ld_cg16(stage + static_cast<size_t>(src) * kTileElems + r * BN + cv);
+            const uint4 raw = ld_cg16(stage + static_cast<size_t>(src) * kTileElems + off);
             const InT* h = reinterpret_cast<const InT*>(&raw);
 #pragma unroll
             for (int i = 0; i < 8; ++i) acc[i] += tof(h[i]);
           }
-          const int gcol = tile_n * BN + cv;
+          const int gcol = tile_n * BN + j * 8;
           if (p.bias != nullptr) {
 #pragma unroll
-            for (int i = 0; i < 8; ++i)
-              if (gcol + i < p.N) acc[i] += __ldg(p.bias + gcol + i);
+            for (int i = 0; i < 8; ++i) acc[i] += __ldg(p.bias + gcol + i);
           }
           uint4 o;
           o.x = pack2(acc[0], acc[1], InT());
           o.y = pack2(acc[2], acc[3], InT());
           o.z = pack2(acc[4], acc[5], InT());
           o.w = pack2(acc[6], acc[7], InT());
-          *reinterpret_cast<uint4*>(res + r * BN + cv) = o;
-          *reinterpret_cast<uint4*>(out + static_cast<size_t>(tile_m * kBM + r) * p.N + gcol) = o;
+          *reinterpret_cast<uint4*>(res + r * BN + j * 8) = o;
+          *reinterpret_cast<uint4*>(out_tile + static_cast<size_t>(r) * p.N + j * 8) = o;
         }
-        __syncthreads();
-        if (threadIdx.x < p.n && static_cast<int>(threadIdx.x) != p.me) {
+        worker_sync();
+        if (wid < p.n && wid != p.me) {
           __threadfence_system();
-          st_release_sys(p.flags[threadIdx.x] + t, p.epoch);
+          st_release_sys(p.flags[wid] + t, p.epoch);
         }
       } else {
-        // ---- wait for the owner's result, then pull it
-        if (threadIdx.x == 0) {
-          if (!wait_flag(p.flags[p.me] + t, p.epoch, p.status, t)) s_ok = 0;
+        if (!mbar_wait(&full_bar[slot], phase, abort_flag, p.status, kErrPeerFlagTimeout, t)) break;
+        const InT* tile = reinterpret_cast<const InT*>(slots + slot * kTileBytes);
+        for (int v = wid; v < total_vec; v += kWorkers) {
+          const int r = v / vec_per_row, j = v - r * vec_per_row;
+          *reinterpret_cast<uint4*>(out_tile + static_cast<size_t>(r) * p.N + j * 8) =
+              *reinterpret_cast<const uint4*>(tile + r * BN + j * 8);
         }
-        __syncthreads();
-        if (!s_ok) break;
-        const InT* res = reinterpret_cast<const InT*>(p.result[owner]) + static_cast<size_t>(li) * kTileElems;
-        for (int v0 = threadIdx.x; v0 < total_vec; v0 += kGemmThreads * 4) {
-          uint4 buf[4];
-          int rr[4], cc[4];
-#pragma unroll
-          for (int u = 0; u < 4; ++u) {
-            const int v = v0 + u * kGemmThreads;
-            if (v < total_vec) {
-              rr[u] = v / vec_per_row;
-              cc[u] = (v - rr[u] * vec_per_row) * 8;
-              buf[u] = ld_cg16(res + rr[u] * BN + cc[u]);
-            }
-          }
-#pragma unroll
-          for (int u = 0; u < 4; ++u) {
-            const int v = v0 + u * kGemmThreads;
-            if (v < total_vec)
-              *reinterpret_cast<uint4*>(out + static_cast<size_t>(tile_m * kBM + rr[u]) * p.N + tile_n * BN + cc[u]) =
-                  buf[u];
-          }
-        }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&empty_bar[slot]);
+        if (++slot == kPullSlots) { slot = 0; phase ^= 1; }
       }
-      __syncthreads();
     }
     return;
   }
 
   // ================================================================= GEMM CTA
+  uint8_t* epi = smem + kFusedStages * Cfg::kStageBytes;
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(epi + kEpiBytes);
+  uint64_t* empty_bar = full_bar + kFusedStages;
+  uint64_t* tfull_bar = empty_bar + kFusedStages;
+  uint64_t* tempty_bar = tfull_bar + 2;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty_bar + 2);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
   if (threadIdx.x == 0) {
-    for (int s = 0; s < Cfg::kStages; ++s) {
+    for (int s = 0; s < kFusedStages; ++s) {
       mbar_init(&full_bar[s], 1);
       mbar_init(&empty_bar[s], 1);
     }
@@ -244,7 +292,7 @@ gemm_allreduce_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_co
             for (int g = 0; g < BN / 64; ++g)
               tma_load_2d(sb + g * 8192, &tma_b, &full_bar[stage], tile_n * BN + g * 64, kb * kBK);
           }
-          if (++stage == Cfg::kStages) { stage = 0; phase ^= 1; }
+          if (++stage == kFusedStages) { stage = 0; phase ^= 1; }
         }
       }
     }
@@ -275,15 +323,17 @@ gemm_allreduce_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_co
             tc_mma_f16(d_tmem, da, db, idesc, (kb > 0 || k16 > 0) ? 1u : 0u);
           }
           tc_commit(&empty_bar[stage]);
-          if (++stage == Cfg::kStages) { stage = 0; phase ^= 1; }
+          if (++stage == kFusedStages) { stage = 0; phase ^= 1; }
         }
         if (!ok) break;
         tc_commit(&tfull_bar[acc]);
       }
     }
   } else {
-    // ---- epilogue: partial tile -> owner's staging slot (peer store), then the arrival flag
+    // ---- epilogue: TMEM -> 16-bit -> this warp's shared slab -> ONE 16 KB bulk copy into the owner's staging
+    //      slot (peer memory), then the arrival flag
     const int quarter = warp & 3;
+    uint8_t* slab = epi + quarter * kSlabBytes;
     int it = 0;
     for (int w = blockIdx.x; w < num_tiles && !*abort_flag; w += G, ++it) {
       int tile_m, tile_n, kb0, kb1;
@@ -294,30 +344,35 @@ gemm_allreduce_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_co
       tc_fence_after();
       const int owner = w % p.n;
       const int li = w / p.n;
-      InT* slot = reinterpret_cast<InT*>(p.stage[owner]) + (static_cast<size_t>(li) * p.n + p.me) * kTileElems;
-      const int r = quarter * 32 + lane;
-      const bool row_ok = tile_m * kBM + r < p.M;
 #pragma unroll 1
       for (int c = 0; c < BN / 32; ++c) {
         if (tile_n * BN + c * 32 >= p.N) break;
         uint32_t raw[32];
         tmem_ld_32x32(tmem_base + acc * BN + c * 32 + (static_cast<uint32_t>(quarter * 32) << 16), raw);
         tmem_wait_ld();
-        if (row_ok) {
-          float v[32];
 #pragma unroll
-          for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(raw[j]);
-          store_row<InT>(slot + r * BN + c * 32, v, true, 32);
+        for (int q = 0; q < 4; ++q) {
+          uint4 u;
+          u.x = pack2(__uint_as_float(raw[q * 8 + 0]), __uint_as_float(raw[q * 8 + 1]), InT());
+          u.y = pack2(__uint_as_float(raw[q * 8 + 2]), __uint_as_float(raw[q * 8 + 3]), InT());
+          u.z = pack2(__uint_as_float(raw[q * 8 + 4]), __uint_as_float(raw[q * 8 + 5]), InT());
+          u.w = pack2(__uint_as_float(raw[q * 8 + 6]), __uint_as_float(raw[q * 8 + 7]), InT());
+          *reinterpret_cast<uint4*>(slab + staged_off(lane, c * 4 + q) * 2) = u;
         }
       }
       tc_fence_before();
+      fence_proxy_async();
       __syncwarp();
       if (lane == 0) {
-        mbar_arrive(&tempty_bar[acc]);
+        mbar_arrive(&tempty_bar[acc]);           // the accumulator can be refilled while the copy is in flight
+        InT* slot = reinterpret_cast<InT*>(p.stage[owner]) + (static_cast<size_t>(li) * p.n + p.me) * kTileElems;
+        bulk_store(slot + quarter * 32 * BN, slab, kSlabBytes);
+        bulk_commit_group();
+        bulk_wait_group0();                      // written, not merely read: the flag must not overtake the data
         __threadfence_system();
-        // the arrival word lives in the owner's flag buffer
         st_release_sys(p.flags[owner] + p.done_cap + (static_cast<size_t>(li) * p.n + p.me) * 4 + quarter, p.epoch);
       }
+      __syncwarp();                              // the slab is free again
     }
   }
 
@@ -334,14 +389,13 @@ gemm_allreduce_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_co
 
 template <bool AK, bool BK_, typename InT>
 static void launch_fused(const CUtensorMap& ta, const CUtensorMap& tb, const FusedParams& p, cudaStream_t stream) {
-  using Cfg = GemmCfg<kFusedBN>;
   auto kern = gemm_allreduce_kernel<AK, BK_, InT>;
   static bool configured = false;
   if (!configured) {
-    C10_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes));
+    C10_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kFusedSmemBytes));
     configured = true;
   }
-  kern<<<p.num_gemm_ctas + p.num_comm_ctas, kGemmThreads, Cfg::kSmemBytes, stream>>>(ta, tb, p);
+  kern<<<p.num_gemm_ctas + p.num_comm_ctas, kGemmThreads, kFusedSmemBytes, stream>>>(ta, tb, p);
   C10_CUDA_KERNEL_LAUNCH_CHECK();
 }
 

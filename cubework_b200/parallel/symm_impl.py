@@ -80,7 +80,7 @@ def _comm_ctas(M, N, K, n):
     t_gemm = 2.0 * M * N * K / 1.4e15
     t_link = 2.0 * (n - 1) / n * M * N * 2 / 700e9
     frac = t_link / (t_link + t_gemm)
-    return int(min(96, max(16, round(148 * frac * 0.75))))
+    return int(min(40, max(12, round(148 * frac * 0.3))))
 
 
 def fused_gemm_all_reduce(a, b, trans_a, trans_b, mode, bias, out_dtype):
