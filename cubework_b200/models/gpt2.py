@@ -10,6 +10,7 @@ import torch
 import torch.nn as nn
 
 from .. import module as cube_nn
+from ..parallel.loss import IGNORE_INDEX
 from .common import MLP, SelfAttention, key_bias_from_mask, maybe_checkpoint, normal_init
 
 
@@ -63,9 +64,11 @@ class GPT2LMLoss(nn.Module):
         self.loss = cube_nn.CrossEntropyLoss()
 
     def forward(self, logits, labels):
-        shift_logits = logits[..., :-1, :].contiguous()
-        shift_labels = labels[..., 1:].contiguous()
-        return self.loss(shift_logits.view(-1, shift_logits.size(-1)), shift_labels.view(-1))
+        # logits at position t are scored against the label at t+1; instead of copying the logits without their
+        # last position, the labels are shifted and the last position of every sequence is marked as ignored
+        pad = labels.new_full(labels.shape[:-1] + (1, ), IGNORE_INDEX)
+        shift_labels = torch.cat([labels[..., 1:], pad], dim=-1)
+        return self.loss(logits.reshape(-1, logits.size(-1)), shift_labels.reshape(-1))
 
 
 class GPT2(nn.Module):

@@ -71,7 +71,63 @@ static torch::Tensor probe_wait(torch::Tensor flag, int64_t epoch, double limit_
   return result;
 }
 
+// Streaming copy src -> dst through shared memory with bulk copies only (one issuing thread per CTA, `kDepth`
+// chunks in flight).  Either pointer may be a peer mapping, which makes this the measuring stick for what the
+// bulk-copy data path of the fused kernels can reach over NVLink.
+constexpr int kCopyDepth = 4;
+__global__ void __launch_bounds__(32) bulk_copy_kernel(uint8_t* dst, const uint8_t* src, size_t bytes, int chunk) {
+  extern __shared__ __align__(128) uint8_t cp_smem[];
+  __shared__ uint64_t bars[kCopyDepth];
+  if (threadIdx.x != 0) return;
+  for (int i = 0; i < kCopyDepth; ++i) mbar_init(&bars[i], 1);
+  fence_barrier_init();
+  const size_t n_chunks = bytes / chunk;
+  volatile int abort_flag = 0;
+  size_t issued = 0, done = 0;
+  uint32_t phase[kCopyDepth] = {0, 0, 0, 0};
+  // chunk ids of this CTA: blockIdx.x, + gridDim.x, ...
+  auto chunk_id = [&](size_t k) { return blockIdx.x + k * gridDim.x; };
+  while (chunk_id(done) < n_chunks) {
+    while (issued < done + kCopyDepth && chunk_id(issued) < n_chunks) {
+      const int s = issued % kCopyDepth;
+      if (issued >= kCopyDepth) {
+        // the store that last used this slot must have finished reading it
+        asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(kCopyDepth - 1) : "memory");
+      }
+      mbar_expect_tx(&bars[s], chunk);
+      asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+                       smem_u32(cp_smem + s * chunk)),
+                   "l"(src + chunk_id(issued) * chunk), "r"(chunk), "r"(smem_u32(&bars[s]))
+                   : "memory");
+      ++issued;
+    }
+    const int s = done % kCopyDepth;
+    if (!mbar_wait(&bars[s], phase[s], &abort_flag, nullptr, 0, 0)) return;
+    phase[s] ^= 1;
+    asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(dst + chunk_id(done) * chunk),
+                 "r"(smem_u32(cp_smem + s * chunk)), "r"(chunk)
+                 : "memory");
+    asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+    ++done;
+  }
+  asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
+}
+
+static void bulk_copy(int64_t dst, int64_t src, int64_t bytes, int64_t chunk, int64_t ctas) {
+  TORCH_CHECK(bytes % chunk == 0 && chunk % 16 == 0 && chunk * kCopyDepth <= 200 * 1024);
+  static bool configured = false;
+  if (!configured) {
+    C10_CUDA_CHECK(cudaFuncSetAttribute(bulk_copy_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+    configured = true;
+  }
+  bulk_copy_kernel<<<static_cast<int>(ctas), 32, chunk * kCopyDepth, at::cuda::getCurrentCUDAStream()>>>(
+      reinterpret_cast<uint8_t*>(dst), reinterpret_cast<const uint8_t*>(src), static_cast<size_t>(bytes),
+      static_cast<int>(chunk));
+  C10_CUDA_KERNEL_LAUNCH_CHECK();
+}
+
 void register_comm(py::module& m) {
+  m.def("bulk_copy", &bulk_copy);
   m.def("probe_wait", &probe_wait);
   m.def("ipc_alloc", &ipc_alloc);
   m.def("ipc_open", &ipc_open);

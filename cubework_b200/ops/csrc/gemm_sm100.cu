@@ -45,6 +45,23 @@ CUtensorMap make_tma_2d(const void* ptr, uint64_t rows, uint64_t cols, uint64_t 
   return m;
 }
 
+// 2-D map without swizzle over a row-major 16-bit matrix, box = box_cols x box_rows (dense rows in shared memory);
+// used for tile stores, which clip the box against the matrix extent.
+CUtensorMap make_tma_2d_plain(const void* ptr, uint64_t rows, uint64_t cols, uint64_t ld, uint32_t box_cols,
+                              uint32_t box_rows) {
+  TORCH_CHECK((reinterpret_cast<uintptr_t>(ptr) & 15) == 0 && (ld * 2) % 16 == 0, "TMA store target must be 16-byte aligned");
+  CUtensorMap m;
+  cuuint64_t dims[2] = {cols, rows};
+  cuuint64_t strides[1] = {ld * 2};
+  cuuint32_t box[2] = {box_cols, box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = get_encode()(&m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, estr,
+                            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_NONE,
+                            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  TORCH_CHECK(r == CUDA_SUCCESS, "cuTensorMapEncodeTiled (plain) failed with code ", static_cast<int>(r));
+  return m;
+}
+
 // 4-D map over 16-bit data [d3][d2][d1][d0] (d0 innermost, strides in bytes for d1..d3), box = 64 x 128 x 1 x 1.
 // Reads past any extent are zero-filled, which is how tiles get their padding.
 CUtensorMap make_tma_4d(const void* ptr, uint64_t d0, uint64_t d1, uint64_t d2, uint64_t d3, uint64_t s1, uint64_t s2,

@@ -31,8 +31,12 @@ def merge_ce_stats(blocks):
     return gmax, gsum, tl.sum(dim=0)
 
 
+IGNORE_INDEX = -100
+
+
 class _ShardedCrossEntropy(torch.autograd.Function):
-    """Per-row loss of logits whose class dimension is split over ``mode`` (or not split: ``None``)."""
+    """Per-row loss of logits whose class dimension is split over ``mode`` (or not split: ``None``).
+    Rows whose target is ``IGNORE_INDEX`` get zero loss and zero gradient."""
 
     @staticmethod
     def forward(ctx, logits, targets, mode):
@@ -47,7 +51,8 @@ class _ShardedCrossEntropy(torch.autograd.Function):
         else:
             blocks = stats.unsqueeze(0)
         gmax, gsum, tl = merge_ce_stats(blocks)
-        loss = torch.log(gsum) + gmax - tl
+        valid = t1 != IGNORE_INDEX
+        loss = (torch.log(gsum) + gmax - tl) * valid
         ctx.save_for_backward(l2, t1, gmax, gsum)
         ctx.vocab_start, ctx.shape, ctx.dtype = vocab_start, logits.shape, cd
         return loss.view(targets.shape)
@@ -55,12 +60,19 @@ class _ShardedCrossEntropy(torch.autograd.Function):
     @staticmethod
     def backward(ctx, g):
         l2, t1, gmax, gsum = ctx.saved_tensors
-        grad = ops.ce_grad(l2, t1, ctx.vocab_start, gmax, gsum, g.reshape(-1).float().contiguous())
+        scale = g.reshape(-1).float() * (t1 != IGNORE_INDEX)
+        grad = ops.ce_grad(l2, t1, ctx.vocab_start, gmax, gsum, scale.contiguous())
         return grad.view(ctx.shape), None, None
 
 
 def sharded_cross_entropy(logits, targets, mode=None):
     return _ShardedCrossEntropy.apply(logits, targets, mode)
+
+
+def masked_mean(loss, targets):
+    """Mean over the rows whose target is not ``IGNORE_INDEX``."""
+    valid = (targets.reshape(-1) != IGNORE_INDEX).sum().clamp_min(1)
+    return loss.sum() / valid
 
 
 class _LossBase(nn.Module):
@@ -75,31 +87,33 @@ class CrossEntropyLossSTD(_LossBase):
 
     def forward(self, logits, targets):
         loss = sharded_cross_entropy(logits, targets, None)
-        return loss.mean() if self.reduction_mean else loss
+        return masked_mean(loss, targets) if self.reduction_mean else loss
 
 
 class VocabParallelCrossEntropyLoss1D(_LossBase):
 
     def forward(self, logits, targets):
         loss = sharded_cross_entropy(logits, targets, pm.PARALLEL_1D)
-        return loss.mean() if self.reduction_mean else loss
+        return masked_mean(loss, targets) if self.reduction_mean else loss
 
 
 class CrossEntropyLoss2D(_LossBase):
 
     def forward(self, logits, targets):
-        loss = sharded_cross_entropy(logits, split_batch_2d(targets), None)
+        targets = split_batch_2d(targets)
+        loss = sharded_cross_entropy(logits, targets, None)
         if self.reduction_mean:
-            loss = reduce_by_batch_2d(loss.mean(), True)
+            loss = reduce_by_batch_2d(masked_mean(loss, targets), True)
         return loss
 
 
 class VocabParallelCrossEntropyLoss2D(_LossBase):
 
     def forward(self, logits, targets):
-        loss = sharded_cross_entropy(logits, split_batch_2d(targets), pm.PARALLEL_2D_ROW)
+        targets = split_batch_2d(targets)
+        loss = sharded_cross_entropy(logits, targets, pm.PARALLEL_2D_ROW)
         if self.reduction_mean:
-            loss = reduce_by_batch_2d(loss.mean(), True)
+            loss = reduce_by_batch_2d(masked_mean(loss, targets), True)
         return loss
 
 
@@ -111,9 +125,10 @@ class _Loss3D(_LossBase):
         self.weight_parallel_mode = get_weight_parallel_mode()
         self.output_parallel_mode = get_output_parallel_mode()
 
-    def _finish(self, loss):
+    def _finish(self, loss, targets):
         if self.reduction_mean:
-            loss = reduce_by_batch_3d(loss.mean(), self.input_parallel_mode, self.weight_parallel_mode, True)
+            loss = reduce_by_batch_3d(masked_mean(loss, targets), self.input_parallel_mode,
+                                      self.weight_parallel_mode, True)
         return loss
 
     def _targets(self, targets):
@@ -123,13 +138,15 @@ class _Loss3D(_LossBase):
 class CrossEntropyLoss3D(_Loss3D):
 
     def forward(self, logits, targets):
-        return self._finish(sharded_cross_entropy(logits, self._targets(targets), None))
+        targets = self._targets(targets)
+        return self._finish(sharded_cross_entropy(logits, targets, None), targets)
 
 
 class VocabParallelCrossEntropyLoss3D(_Loss3D):
 
     def forward(self, logits, targets):
-        return self._finish(sharded_cross_entropy(logits, self._targets(targets), self.output_parallel_mode))
+        targets = self._targets(targets)
+        return self._finish(sharded_cross_entropy(logits, targets, self.output_parallel_mode), targets)
 
 
 _parallel_cross_entropy = {None: CrossEntropyLossSTD, "1d": CrossEntropyLossSTD, "2d": CrossEntropyLoss2D,

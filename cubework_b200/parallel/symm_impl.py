@@ -17,6 +17,7 @@ _STAGE_BYTES = int(os.environ.get("CUBEWORK_B200_STAGE_MB", "160")) << 20
 _RESULT_BYTES = int(os.environ.get("CUBEWORK_B200_RESULT_MB", "64")) << 20
 _DONE_CAP = 1 << 16          # tiles per call
 _COMM_CTAS = int(os.environ.get("CUBEWORK_B200_COMM_CTAS", "0"))
+TRACE = None                  # optional int64 [148, 192, 2] CUDA tensor: per-CTA event trace of the next fused launches
 
 
 class Workspace:
@@ -28,7 +29,7 @@ class Workspace:
         self.me = mode.local_rank
         self.epoch = 0
         self.owned_cap = min(_RESULT_BYTES // TILE_BYTES, _STAGE_BYTES // (TILE_BYTES * self.n))
-        flag_bytes = 4 * (_DONE_CAP + self.owned_cap * self.n * 4)
+        flag_bytes = 4 * (_DONE_CAP * 8 + self.owned_cap * self.n * 8)
         self._local = []
         self._opened = []
         self.ptrs = {}
@@ -80,7 +81,7 @@ def _comm_ctas(M, N, K, n):
     t_gemm = 2.0 * M * N * K / 1.4e15
     t_link = 2.0 * (n - 1) / n * M * N * 2 / 700e9
     frac = t_link / (t_link + t_gemm)
-    return int(min(40, max(12, round(148 * frac * 0.3))))
+    return int(min(32, max(8, round(148 * frac * 0.15))))
 
 
 def fused_gemm_all_reduce(a, b, trans_a, trans_b, mode, bias, out_dtype):
@@ -101,7 +102,7 @@ def fused_gemm_all_reduce(a, b, trans_a, trans_b, mode, bias, out_dtype):
     ext._count(1)
     m.fused_gemm_all_reduce(a, b, bool(trans_a), bool(trans_b), bias, out, ws.ptrs["stage"], ws.ptrs["result"],
                             ws.ptrs["flags"], _DONE_CAP, ws.me, ws.epoch, _comm_ctas(M, N, K, ws.n),
-                            m.status_device_ptr())
+                            m.status_device_ptr(), TRACE)
     from . import collective
     if collective._profiler is not None:
         collective._profiler.account("fused_gemm_all_reduce", 2 * (ws.n - 1) * M * N * a.element_size() // ws.n)

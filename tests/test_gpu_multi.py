@@ -126,6 +126,14 @@ def test_fused_gemm_all_reduce_two_ranks():
     _multi(_check_fused_all_reduce)
 
 
+def test_fused_gemm_all_reduce_every_gpu():
+    """Same check over all GPUs of the box (4 or 8 ranks: the two-shot schedule has n-1 push tiles per group)."""
+    n = torch.cuda.device_count()
+    if n < 4:
+        pytest.skip("needs at least 4 GPUs")
+    _multi(_check_fused_all_reduce, 8 if n >= 8 else 4)
+
+
 def test_1d_layers_bf16_two_ranks():
     _multi(_check_layers_bf16)
 
