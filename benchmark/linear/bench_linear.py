@@ -111,6 +111,7 @@ def main():
         res = {}
         for label, fused_on in (("fused", True), ("nccl+own-gemm", False)):
             symm._DISABLED = not fused_on
+            symm._POLICY = "1" if fused_on else "0"
             res[label] = time_fb(layer, x)
         os.environ["CUBEWORK_B200_KERNELS"] = "0"
         res["nccl+cublas"] = time_fb(layer, x)

@@ -66,3 +66,18 @@ def gather_gemm_reduce(a: torch.Tensor, b: torch.Tensor, trans_a: bool = False, 
 
 def gemm_all_reduce(a, b, trans_a, trans_b, mode, bias=None, out_dtype=None):
     return gather_gemm_reduce(a, b, trans_a, trans_b, reduce=mode, bias=bias, out_dtype=out_dtype)
+
+
+def gemm_all_reduce_async(a, b, trans_a, trans_b, mode, out_dtype=None):
+    """``(C, work)``: like :func:`gemm_all_reduce`, but when the fused kernel is not used the all-reduce is
+    started asynchronously and ``work.wait()`` must be called before ``C`` is read - the caller runs an
+    independent GEMM (the weight gradient) in between.  ``work`` is None when nothing is pending."""
+    out_dtype = out_dtype or a.dtype
+    if ops.use_kernels(a) and symm.available():
+        res = symm.fused_gather_gemm_reduce(a, b, trans_a, trans_b, None, None, None, mode, None, out_dtype, False)
+        if res is not None:
+            return res, None
+    c = ops.gemm(a, b, trans_a, trans_b, out_dtype=out_dtype)
+    if mode.world_size > 1:
+        return all_reduce(c, mode, async_op=True)
+    return c, None

@@ -142,18 +142,23 @@ class _Linear1D(torch.autograd.Function):
         if db is not None:
             db = db.to(ctx.bias_dtype)
         dx = None
+        pending = None
         if ctx.needs_input_grad[0]:
             wc = ops.shadow(w, cd)
             if ctx.reduce_bwd and ctx.mode.world_size > 1:
-                dx = fused.gemm_all_reduce(dy2, wc, False, False, ctx.mode)
+                # fused GEMM+all-reduce, or GEMM + an all-reduce that runs behind the weight-gradient GEMM below
+                dx, pending = fused.gemm_all_reduce_async(dy2, wc, False, False, ctx.mode)
             else:
                 dx = ops.gemm(dy2, wc)
-            dx = dx.view(ctx.x_shape)
-            if dx.dtype != ctx.x_dtype:
-                dx = dx.to(ctx.x_dtype)
         dw = None
         if ctx.needs_input_grad[1]:
             dw = ops.gemm(dy2, x2, trans_a=True, out_dtype=w.dtype)
+        if pending is not None:
+            pending.wait()
+        if dx is not None:
+            dx = dx.view(ctx.x_shape)
+            if dx.dtype != ctx.x_dtype:
+                dx = dx.to(ctx.x_dtype)
         return dx, dw, db, None, None, None, None
 
 

@@ -92,6 +92,9 @@ def fused_gemm_all_reduce(a, b, trans_a, trans_b, mode, bias, out_dtype):
     N = b.shape[0] if trans_b else b.shape[1]
     if N % 8 != 0 or a.shape[1] % 8 != 0 or b.shape[1] % 8 != 0 or mode.world_size > 8:
         return None
+    from . import symm
+    if not symm.prefer_fused(M, N, K, mode.world_size):
+        return None
     ws = workspace(mode)
     if not ws.fits(M, N):
         return None

@@ -31,6 +31,7 @@ def _check_fused_all_reduce():
     from cubework_b200.ops import ext
     from cubework_b200.parallel import fused, symm
     assert symm.available()
+    symm._POLICY = "1"          # always take the fused kernel here, whatever the size heuristic says
     mode = pm.PARALLEL_1D
     n, r = mode.world_size, mode.local_rank
     dev = torch.device("cuda", torch.cuda.current_device())
