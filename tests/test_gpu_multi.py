@@ -117,10 +117,55 @@ def _check_gpt2_step():
     assert abs(losses[0] - 7.62) < 0.2 and losses[2] < losses[0], losses
 
 
-def _multi(fn, n=2):
+def _check_model_against_cpu_oracle(family):
+    """bf16 kernel path of a tiny model under the active tensor-parallel mode vs the unsharded fp32 model on the host."""
+    from cubework_b200.engine import Trainer
+    from cubework_b200.global_vars import env
+    from cubework_b200.ops import ext
+    from cubework_b200.optim import FusedAdamW
+    from cubework_b200.utils import checkpoint as ck
+    import test_models as tm
+    dev = torch.device("cuda", torch.cuda.current_device())
+    saved = env.save()
+    env.load(mode=None)
+    master, mcrit = tm._build(family)
+    tm._init_002(master)
+    init_sd = {k: v.detach().clone() for k, v in master.state_dict().items()}
+    batch = tm._batch(family)
+    ref = Trainer(master, mcrit, FusedAdamW(master.parameters(), lr=1e-3), amp_dtype=None, device=torch.device("cpu"))
+    ref_losses = [ref.step(batch).item() for _ in range(3)]
+    env.load(**saved)
+    model, crit = tm._build(family)
+    model = model.to(dev)
+    ck.load_full_state_dict(model, init_sd)
+    tr = Trainer(model, crit, FusedAdamW(model.parameters(), lr=1e-3), amp_dtype=torch.bfloat16)
+    losses = [tr.step(batch).item() for _ in range(3)]
+    torch.cuda.synchronize()
+    ext.check_status()
+    for a, b in zip(losses, ref_losses):
+        assert abs(a - b) < 0.03 * max(1.0, abs(b)), (family, losses, ref_losses)
+    assert losses[2] < losses[0]
+
+
+def _multi(fn, n=2, tp="1d", args=()):
     _need(n)
     os.environ["NCCL_NVLS_ENABLE"] = "0"
-    run_dist(fn, n, tp="1d", tp_size=n, backend="nccl", use_cuda=True)
+    run_dist(fn, n, tp=tp, tp_size=n, backend="nccl", use_cuda=True, args=args)
+
+
+def test_2d_models_bf16_four_ranks():
+    for family in ("gpt2", "vit"):
+        _multi(_check_model_against_cpu_oracle, 4, tp="2d", args=(family, ))
+
+
+def test_3d_models_bf16_eight_ranks():
+    for family in ("gpt2", "vit"):
+        _multi(_check_model_against_cpu_oracle, 8, tp="3d", args=(family, ))
+
+
+def test_1d_models_bf16_two_ranks():
+    for family in ("gpt2", "opt", "vit"):
+        _multi(_check_model_against_cpu_oracle, 2, tp="1d", args=(family, ))
 
 
 def test_fused_gemm_all_reduce_two_ranks():
