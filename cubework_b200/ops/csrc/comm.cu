@@ -12,6 +12,7 @@ namespace py = pybind11;
 namespace cw {
 
 void register_fused(py::module& m);
+void register_ggs(py::module& m);
 
 // Allocate `nbytes` with cudaMalloc (outside the caching allocator, so the IPC handle maps exactly this
 // buffer) and return (device pointer, IPC handle bytes).
@@ -135,6 +136,7 @@ void register_comm(py::module& m) {
   m.def("ipc_free", &ipc_free);
   m.def("as_tensor", &as_tensor);
   register_fused(m);
+  register_ggs(m);
 }
 
 }  // namespace cw

@@ -1,0 +1,729 @@
+// All-gather -> GEMM -> reduce-scatter as ONE kernel per rank: the parallel matmul of the 2D (SUMMA) and 3D
+// layouts, with both collectives moved into the tcgen05 GEMM and carried over NVLink peer memory.
+//
+//   out = reduce-scatter_s( op(gather_a(A)) * op(gather_b(B)) ) + bias
+//
+// Every part is optional: a gathered A and/or B (each over its own process group, concatenated along the
+// rows or the columns of the stored shard), and a reduce-scatter of the product along its rows or columns
+// over a third group.
+//
+// Grid = C communication CTAs + G GEMM CTAs, all co-resident (one CTA per SM).
+//  * communication CTAs push this rank's shard, panel by panel (a panel = a block of stored rows), into the
+//    gather buffer of every rank of the operand's group (its own included) with bulk copies
+//    global -> shared -> peer, and publish one arrival flag per (destination, panel).  They wait for nobody.
+//  * GEMM CTAs run the persistent TMA -> tcgen05 -> TMEM pipeline.  The TMA producer reads a gathered
+//    operand from the *local* gather buffer [sources][rows][cols]; before the first load that touches a
+//    (source, panel) it waits for that panel's flag (remembered in a shared-memory bitmap afterwards).  The
+//    K loop starts at the k-blocks of the local shard, so multiplication begins while remote panels are
+//    still in flight.
+//  * with a reduce-scatter, tile ownership follows the output shard: "push" CTAs compute tiles of other
+//    owners and send the 16-bit partials into the owner's staging buffer (8 KB bulk copies, flags batched
+//    behind one system-scope fence by a publisher thread); "own" CTAs compute this rank's tiles, wait for
+//    the other ranks' partials, add them in fp32 to the accumulator (+ bias) and store the output shard.
+// Gather and staging buffers are used in two halves that alternate with the call epoch: a rank can run at
+// most one call ahead of a peer (it needs that peer's data of the current call to finish), so the half
+// written now was last read two calls ago.  Flags hold epochs that only grow.  Every wait is bounded and
+// reports to the status word.  TMA tensor maps cover local memory only; peer memory is touched by bulk
+// copies and plain stores.
+//
+// The reference runs these as separate NCCL collectives around cuBLAS GEMMs: q rounds of broadcast + addmm in
+// cubework/module/parallel_2d/_operation.py:15-239, all_gather / matmul / reduce_scatter in
+// cubework/module/parallel_3d/_operation.py:12-68.
+#include <ATen/cuda/CUDAContext.h>
+#include <c10/cuda/CUDAGuard.h>
+#include <pybind11/pybind11.h>
+#include <torch/extension.h>
+
+#include "fused_common.cuh"
+
+namespace py = pybind11;
+
+namespace cw {
+
+constexpr int kKnownWords = 64;            // 2048 (source, panel) arrival bits per operand
+constexpr int kPiece = 32 * 1024;          // bytes per bulk copy of the gather pushers
+constexpr int kPushSlots = 6;              // shared-memory pieces in flight per communication CTA
+constexpr int kPendItems = 16;
+static_assert(kPushSlots * kPiece + 1024 + 256 <= kFusedSmemBytes, "push slots must fit the GEMM allocation");
+
+struct GatherView {          // how the TMA producer sees one operand
+  int live;                  // 0: an ordinary local tensor, nothing to wait for
+  int n;                     // sources
+  int g;                     // stored dimension along which the shards are concatenated (0 rows, 1 columns)
+  int R, C;                  // extent of one stored shard
+  int panel_rows, panels;    // one arrival flag per `panel_rows` stored rows of a source
+  int epoch;
+  const int* flags;          // local [n][panels]
+};
+
+struct GatherPush {          // what the communication CTAs do for one operand
+  int live, n, me, panels, epoch;
+  long long shard_bytes, panel_bytes;
+  const uint8_t* src;        // this rank's shard, dense [R][C] 16-bit
+  uint8_t* dst[kMaxRanks];   // every rank's gather buffer (own included): [n][R][C]
+  int* flags[kMaxRanks];     // every rank's flag array [n][panels]
+};
+
+struct GgsParams {
+  int M, N, K;               // the product this rank computes: [M, K] x [K, N]
+  int num_comm_ctas, num_gemm_ctas;
+  int is_bf16;
+  uint32_t mn_lbo, mn_sbo;
+  int k_start;               // first k-block of the loop (the local shard's, when K is gathered)
+  int b_first;               // push B's panels before A's
+  GatherView va, vb;
+  GatherPush pa, pb;
+  int sc_dim;                // reduce-scatter of the product: -1 none, 0 rows, 1 columns
+  int sn, sme, sepoch;
+  int Ms, Ns;                // extent of one owner's part of the product
+  int tiles_m, tiles_n;      // tile grid of one owner's part
+  void* stage[kMaxRanks];    // [owned tiles][sn][128 x 256] 16-bit, this call's half
+  int* sflags[kMaxRanks];    // [owned tiles][sn][8]
+  void* out;                 // local [Ms or M][ldo]
+  int ldo;
+  const float* bias;         // optional, indexed by output column
+  int* status;
+};
+
+__device__ __forceinline__ void fence_proxy_async_all() { asm volatile("fence.proxy.async;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void bulk_wait_group_n() {
+  asm volatile("cp.async.bulk.wait_group %0;" ::"n"(N) : "memory");
+}
+
+// Completed pushes waiting for their flag: written by the storing thread, drained by the publisher.
+struct PushBox {
+  int* volatile item[kPendItems * 2];
+  volatile int tail, head, finished;
+};
+
+struct TileInfo {
+  int row0, col0;     // position in the product
+  int rows, cols;     // valid extent
+  int orow, ocol;     // position in the local output
+};
+
+__device__ __forceinline__ TileInfo tile_info(const GgsParams& p, int owner, int li, int kb_total) {
+  int tm, tn, kb0, kb1;
+  decode_work(li, p.tiles_m * p.tiles_n, p.tiles_m, p.tiles_n, kb_total, 1, tm, tn, kb0, kb1);
+  TileInfo t;
+  t.orow = tm * kBM;
+  t.ocol = tn * kFusedBN;
+  t.row0 = (p.sc_dim == 0 ? owner * p.Ms : 0) + t.orow;
+  t.col0 = (p.sc_dim == 1 ? owner * p.Ns : 0) + t.ocol;
+  t.rows = min(kBM, p.Ms - t.orow);
+  t.cols = min(kFusedBN, p.Ns - t.ocol);
+  return t;
+}
+
+// rows [r0, r1) of source s must have arrived
+__device__ __forceinline__ bool ensure_panels(const GatherView& v, uint32_t* known, int s, int r0, int r1, int* status) {
+  if (r1 <= r0) return true;
+  for (int pnl = r0 / v.panel_rows; pnl <= (r1 - 1) / v.panel_rows; ++pnl) {
+    const int idx = s * v.panels + pnl;
+    if ((known[idx >> 5] >> (idx & 31)) & 1u) continue;
+    if (!wait_flag(v.flags + idx, v.epoch, status, idx)) return false;
+    fence_proxy_async_all();                      // the TMA reads that follow must see what the flag announced
+    known[idx >> 5] |= 1u << (idx & 31);
+  }
+  return true;
+}
+// rows [y0, y1) of the concatenation along the rows (g == 0)
+__device__ __forceinline__ bool ensure_stacked(const GatherView& v, uint32_t* known, int y0, int y1, int* status) {
+  y1 = min(y1, v.n * v.R);
+  while (y0 < y1) {
+    const int s = y0 / v.R, r = y0 - s * v.R;
+    const int len = min(v.R - r, y1 - y0);
+    if (!ensure_panels(v, known, s, r, r + len, status)) return false;
+    y0 += len;
+  }
+  return true;
+}
+
+// Coordinates of one TMA box of an operand + the arrival check.  (x, y) = (column, row) of the box in the full
+// (gathered) stored operand, h = rows of the box.  Boxes are 64 columns wide and, along a column-wise
+// concatenation, never straddle two sources (the host checks the divisibility that guarantees it).
+__device__ __forceinline__ bool locate(const GatherView& v, uint32_t* known, int& x, int& y, int h, int* status) {
+  if (!v.live) return true;
+  if (v.g == 0) return ensure_stacked(v, known, y, y + h, status);
+  const int s = x / v.C;
+  if (s >= v.n) return true;                     // beyond the operand: the load is zero-filled
+  x -= s * v.C;
+  const bool ok = ensure_panels(v, known, s, min(y, v.R), min(y + h, v.R), status);
+  y += s * v.R;
+  return ok;
+}
+
+template <bool A_KMAJOR, bool B_KMAJOR, typename InT, bool OUT_F32>
+__global__ void __launch_bounds__(kGemmThreads, 1)
+gather_gemm_scatter_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
+                           const __grid_constant__ GgsParams p) {
+  constexpr int BN = kFusedBN;
+  using Cfg = GemmCfg<BN>;
+  using OutT = typename OutType<InT, OUT_F32>::type;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int kb_total = (p.K + kBK - 1) / kBK;
+  const bool is_comm = static_cast<int>(blockIdx.x) < p.num_comm_ctas;
+
+  if (is_comm) {
+    // =========================================================== communication CTA: push this rank's shards
+    // three single threads: loader (global -> shared), storer (shared -> destination), publisher (flags)
+    uint8_t* slots = smem;
+    uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + kPushSlots * kPiece);
+    uint64_t* empty_bar = full_bar + kPushSlots;
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(empty_bar + kPushSlots);
+    __shared__ PushBox box;
+    if (threadIdx.x == 0) {
+      for (int s = 0; s < kPushSlots; ++s) {
+        mbar_init(&full_bar[s], 1);
+        mbar_init(&empty_bar[s], 1);
+      }
+      *abort_flag = 0;
+      box.tail = 0; box.head = 0; box.finished = 0;
+      fence_barrier_init();
+    }
+    __syncthreads();
+    if (warp > 2 || lane != 0) return;
+    const int c = blockIdx.x;
+    const GatherPush& first = p.b_first ? p.pb : p.pa;
+    const GatherPush& second = p.b_first ? p.pa : p.pb;
+    const int n_first = first.live ? first.panels * first.n : 0;
+    const int n_second = second.live ? second.panels * second.n : 0;
+
+    if (warp == 2) {
+      // ---- publisher
+      const unsigned long long t_start = globaltimer_ns();
+      int head = 0;
+      for (;;) {
+        const int fin = box.finished;
+        const int tail = box.tail;
+        if (head == tail) {
+          if (fin || *abort_flag) {
+            if (head == box.tail) break;
+            continue;
+          }
+          if (globaltimer_ns() - t_start > 4 * kWaitLimitNs) break;
+          __nanosleep(100);
+          continue;
+        }
+        __threadfence_block();
+        __threadfence_system();
+        for (; head < tail; ++head) {
+          int* f = box.item[head % (kPendItems * 2)];
+          const GatherPush& op = (reinterpret_cast<uintptr_t>(f) & 1) ? second : first;
+          st_relaxed_sys(reinterpret_cast<int*>(reinterpret_cast<uintptr_t>(f) & ~uintptr_t(1)), op.epoch);
+        }
+        box.head = head;
+      }
+      return;
+    }
+
+    int slot = 0;
+    uint32_t phase = 0;
+    int seq = -1;                                   // storer: index of the bulk group committed last
+    int box_tail = 0;
+    bool ok = true;
+    for (int i = c; i < n_first + n_second && ok; i += p.num_comm_ctas) {
+      const bool is_second = i >= n_first;
+      const GatherPush& op = is_second ? second : first;
+      const int idx = is_second ? i - n_first : i;
+      const int panel = idx / op.n;
+      const int dest = (op.me + idx % op.n) % op.n;
+      const long long off0 = static_cast<long long>(panel) * op.panel_bytes;
+      const long long bytes = min(op.panel_bytes, op.shard_bytes - off0);
+      const uint8_t* src = op.src + off0;
+      uint8_t* dst = op.dst[dest] + static_cast<long long>(op.me) * op.shard_bytes + off0;
+      for (long long off = 0; off < bytes; off += kPiece) {
+        const uint32_t len = static_cast<uint32_t>(min(static_cast<long long>(kPiece), bytes - off));
+        if (warp == 0) {
+          if (!mbar_wait(&empty_bar[slot], phase ^ 1, abort_flag, p.status, kErrEmptyBarrierTimeout, i)) { ok = false; break; }
+          mbar_expect_tx(&full_bar[slot], len);
+          bulk_load(slots + slot * kPiece, src + off, len, &full_bar[slot]);
+        } else {
+          if (!mbar_wait(&full_bar[slot], phase, abort_flag, p.status, kErrFullBarrierTimeout, i)) { ok = false; break; }
+          bulk_store(dst + off, slots + slot * kPiece, len);
+          bulk_commit_group();
+          ++seq;
+          bulk_wait_group_read_n<2>();              // groups <= seq-2 no longer read their slot: hand it back
+          if (seq >= 2) mbar_arrive(&empty_bar[(slot + kPushSlots - 2) % kPushSlots]);
+        }
+        if (++slot == kPushSlots) { slot = 0; phase ^= 1; }
+      }
+      if (warp == 1 && ok) {
+        // the panel is complete at its destination: hand its flag to the publisher (the loader keeps prefetching
+        // the next panel into free slots meanwhile)
+        bulk_wait_group0();
+        for (int spin = 0; box_tail - box.head >= kPendItems * 2 && spin < (1 << 22); ++spin) __nanosleep(50);
+        int* f = op.flags[dest] + op.me * op.panels + panel;
+        box.item[box_tail % (kPendItems * 2)] =
+            reinterpret_cast<int*>(reinterpret_cast<uintptr_t>(f) | (is_second ? 1u : 0u));
+        __threadfence_block();
+        box.tail = ++box_tail;
+      }
+    }
+    if (warp == 1) {
+      bulk_wait_group0();
+      __threadfence_block();
+      box.finished = 1;
+    }
+    return;
+  }
+
+  // ================================================================= GEMM CTA
+  uint8_t* epi = smem + kFusedStages * Cfg::kStageBytes;
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(epi + kEpiBytes);
+  uint64_t* empty_bar = full_bar + kFusedStages;
+  uint64_t* tfull_bar = empty_bar + kFusedStages;
+  uint64_t* tempty_bar = tfull_bar + 2;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty_bar + 2);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  __shared__ Mailbox mailbox;
+  __shared__ uint32_t known_a[kKnownWords], known_b[kKnownWords];
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kFusedStages; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(&tfull_bar[a], 1);
+      mbar_init(&tempty_bar[a], 4);
+    }
+    *abort_flag = 0;
+    for (int q = 0; q < 4; ++q) { mailbox.tail[q] = 0; mailbox.head[q] = 0; }
+    mailbox.finished = 0;
+    fence_barrier_init();
+    tma_prefetch_desc(&tma_a);
+    tma_prefetch_desc(&tma_b);
+  }
+  if (threadIdx.x >= 32 && threadIdx.x < 32 + kKnownWords) {
+    known_a[threadIdx.x - 32] = 0;
+    known_b[threadIdx.x - 32] = 0;
+  }
+  if (warp == 1) {
+    __syncwarp();
+    tmem_alloc(tmem_slot, Cfg::kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  // role of this CTA and its tile list
+  const bool scat = p.sc_dim >= 0;
+  const int G = p.num_gemm_ctas;
+  const int bid = blockIdx.x - p.num_comm_ctas;
+  const int tpo = p.tiles_m * p.tiles_n;                     // tiles per owner
+  int g_push = 0;
+  if (scat) g_push = max(1, min(G - 1, (G * (p.sn - 1) + p.sn / 2) / p.sn));
+  const int g_own = G - g_push;
+  const bool push_role = bid < g_push;
+  const int n_push_items = scat ? tpo * (p.sn - 1) : 0;
+  auto tile_of = [&](int k, int& owner, int& li) -> bool {   // false: finished
+    if (push_role) {
+      const int item = bid + k * g_push;
+      if (item >= n_push_items) return false;
+      li = item / (p.sn - 1);
+      owner = (p.sme + 1 + item % (p.sn - 1)) % p.sn;
+      return true;
+    }
+    li = (bid - g_push) + k * g_own;
+    owner = scat ? p.sme : 0;
+    return li < tpo;
+  };
+
+  if (warp == 0) {
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      int owner, li;
+      for (int k = 0; !*abort_flag && tile_of(k, owner, li); ++k) {
+        const TileInfo ti = tile_info(p, owner, li, kb_total);
+        bool ok = true;
+        for (int kbi = 0; kbi < kb_total && ok; ++kbi) {
+          int kb = kbi + p.k_start;
+          if (kb >= kb_total) kb -= kb_total;
+          if (!mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag, p.status, kErrEmptyBarrierTimeout, li)) { ok = false; break; }
+          uint8_t* sa = smem + stage * Cfg::kStageBytes;
+          uint8_t* sb = sa + Cfg::kABytes;
+          int ax[2], ay[2], bx[4], by[4];
+          if (A_KMAJOR) {
+            ax[0] = kb * kBK; ay[0] = ti.row0;
+            ok = ok && locate(p.va, known_a, ax[0], ay[0], kBM, p.status);
+          } else {
+#pragma unroll
+            for (int g = 0; g < kBM / 64; ++g) {
+              ax[g] = ti.row0 + g * 64; ay[g] = kb * kBK;
+              ok = ok && locate(p.va, known_a, ax[g], ay[g], kBK, p.status);
+            }
+          }
+          if (B_KMAJOR) {
+            bx[0] = kb * kBK; by[0] = ti.col0;
+            ok = ok && locate(p.vb, known_b, bx[0], by[0], BN, p.status);
+          } else {
+#pragma unroll
+            for (int g = 0; g < BN / 64; ++g) {
+              bx[g] = ti.col0 + g * 64; by[g] = kb * kBK;
+              ok = ok && locate(p.vb, known_b, bx[g], by[g], kBK, p.status);
+            }
+          }
+          if (!ok) { *abort_flag = 1; break; }
+          mbar_expect_tx(&full_bar[stage], Cfg::kStageBytes);
+          if (A_KMAJOR) {
+            tma_load_2d(sa, &tma_a, &full_bar[stage], ax[0], ay[0]);
+          } else {
+#pragma unroll
+            for (int g = 0; g < kBM / 64; ++g) tma_load_2d(sa + g * 8192, &tma_a, &full_bar[stage], ax[g], ay[g]);
+          }
+          if (B_KMAJOR) {
+            tma_load_2d(sb, &tma_b, &full_bar[stage], bx[0], by[0]);
+          } else {
+#pragma unroll
+            for (int g = 0; g < BN / 64; ++g) tma_load_2d(sb + g * 8192, &tma_b, &full_bar[stage], bx[g], by[g]);
+          }
+          if (++stage == kFusedStages) { stage = 0; phase ^= 1; }
+        }
+        if (!ok) break;
+      }
+    } else if (lane == 1 && scat) {
+      // ---- publisher of the partial tiles this CTA pushed: one system-scope fence per batch, then the flags
+      int head[4] = {0, 0, 0, 0};
+      const unsigned long long t_start = globaltimer_ns();
+      for (;;) {
+        int batch[32];
+        int nb = 0;
+        const int fin = mailbox.finished;
+        for (int q = 0; q < 4; ++q) {
+          const int tail = mailbox.tail[q];
+          while (head[q] < tail && nb < 32) {
+            batch[nb++] = mailbox.item[q][head[q] % kMailboxDepth];
+            ++head[q];
+          }
+          mailbox.head[q] = head[q];
+        }
+        if (nb == 0) {
+          if (fin == 4 || *abort_flag) {
+            bool drained = true;
+            for (int q = 0; q < 4; ++q) drained = drained && head[q] == mailbox.tail[q];
+            if (drained) break;
+            continue;
+          }
+          if (globaltimer_ns() - t_start > 4 * kWaitLimitNs) break;
+          __nanosleep(100);
+          continue;
+        }
+        __threadfence_block();
+        __threadfence_system();
+        for (int b = 0; b < nb; ++b) {
+          const int slot_id = batch[b] >> 3, qh = batch[b] & 7;
+          const int owner = slot_id % p.sn, li = slot_id / p.sn;
+          st_relaxed_sys(p.sflags[owner] + (static_cast<size_t>(li) * p.sn + p.sme) * 8 + qh, p.sepoch);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      const uint32_t idesc = make_idesc_f16(kBM, BN, !A_KMAJOR, !B_KMAJOR, p.is_bf16);
+      int stage = 0;
+      uint32_t phase = 0;
+      int it = 0;
+      int owner, li;
+      for (int k = 0; !*abort_flag && tile_of(k, owner, li); ++k) {
+        const int acc = it & 1;
+        const uint32_t acc_phase = (it >> 1) & 1;
+        ++it;
+        if (!mbar_wait(&tempty_bar[acc], acc_phase ^ 1, abort_flag, p.status, kErrTmemEmptyTimeout, li)) break;
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + acc * BN;
+        bool ok = true;
+        for (int kb = 0; kb < kb_total; ++kb) {
+          if (!mbar_wait(&full_bar[stage], phase, abort_flag, p.status, kErrFullBarrierTimeout, li)) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t sa = smem_u32(smem + stage * Cfg::kStageBytes);
+          const uint32_t sb = sa + Cfg::kABytes;
+#pragma unroll
+          for (int k16 = 0; k16 < kBK / 16; ++k16) {
+            const uint64_t da = A_KMAJOR ? make_smem_desc(sa + k16 * 32, 16, 1024)
+                                         : make_smem_desc(sa + k16 * 2048, p.mn_lbo, p.mn_sbo);
+            const uint64_t db = B_KMAJOR ? make_smem_desc(sb + k16 * 32, 16, 1024)
+                                         : make_smem_desc(sb + k16 * 2048, p.mn_lbo, p.mn_sbo);
+            tc_mma_f16(d_tmem, da, db, idesc, (kb > 0 || k16 > 0) ? 1u : 0u);
+          }
+          tc_commit(&empty_bar[stage]);
+          if (++stage == kFusedStages) { stage = 0; phase ^= 1; }
+        }
+        if (!ok) break;
+        tc_commit(&tfull_bar[acc]);
+      }
+    }
+  } else {
+    // ---- epilogue (4 warps, 32 accumulator rows each), per tile in two column halves of 128.
+    //  push role: 16-bit partial -> 8 KB half-slab in shared memory -> one bulk copy into the owner's staging slot
+    //  own role : (wait for and add the other ranks' partials) + bias -> output rows
+    const int quarter = warp & 3;
+    uint8_t* buf = epi + quarter * kHalfSlabBytes;
+    OutT* out = reinterpret_cast<OutT*>(p.out);
+    const bool vec_ok = (p.ldo % (16 / static_cast<int>(sizeof(OutT)))) == 0;
+    int pend = -1;
+    int mb_tail = 0;
+    int it = 0;
+    bool failed = false;
+    int owner, li;
+    for (int k = 0; !*abort_flag && !failed && tile_of(k, owner, li); ++k) {
+      const TileInfo ti = tile_info(p, owner, li, kb_total);
+      const int acc = it & 1;
+      const uint32_t acc_phase = (it >> 1) & 1;
+      ++it;
+      if (!mbar_wait(&tfull_bar[acc], acc_phase, abort_flag, p.status, kErrTmemFullTimeout, li)) break;
+      tc_fence_after();
+      const bool mine = !push_role;
+      const InT* stage = reinterpret_cast<const InT*>(p.stage[scat ? p.sme : 0]) + static_cast<size_t>(li) * p.sn * kTileElems;
+      const int r = quarter * 32 + lane;
+#pragma unroll 1
+      for (int h = 0; h < 2; ++h) {
+        if (h * 128 >= ti.cols) break;                         // warp-uniform
+        if (!mine && lane == 0) bulk_wait_group_read_n<0>();   // the previous copy has finished reading `buf`
+        if (mine && scat) {
+          bool ok = true;
+          if (lane < p.sn && lane != p.sme)
+            ok = wait_flag(p.sflags[p.sme] + (static_cast<size_t>(li) * p.sn + lane) * 8 + quarter * 2 + h, p.sepoch,
+                           p.status, li);
+          if (__any_sync(0xffffffffu, !ok)) { failed = true; break; }
+        }
+        __syncwarp();
+#pragma unroll 1
+        for (int c = 0; c < 4; ++c) {
+          const int c0 = h * 128 + c * 32;
+          if (c0 >= ti.cols) break;
+          uint32_t raw[32];
+          tmem_ld_32x32(tmem_base + acc * BN + c0 + (static_cast<uint32_t>(quarter * 32) << 16), raw);
+          tmem_wait_ld();
+          float v[32];
+#pragma unroll
+          for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(raw[j]);
+          if (mine) {
+            if (scat) {
+              for (int src = 0; src < p.sn; ++src) {
+                if (src == p.sme) continue;
+                uint4 part[4];
+#pragma unroll
+                for (int q = 0; q < 4; ++q)
+                  part[q] = ld_cg16(stage + static_cast<size_t>(src) * kTileElems + staged_off(r, h * 16 + c * 4 + q));
+#pragma unroll
+                for (int q = 0; q < 4; ++q) {
+                  const InT* hh = reinterpret_cast<const InT*>(&part[q]);
+#pragma unroll
+                  for (int e = 0; e < 8; ++e) v[q * 8 + e] += tof(hh[e]);
+                }
+              }
+            }
+            if (p.bias != nullptr) {
+#pragma unroll
+              for (int j = 0; j < 32; ++j)
+                if (c0 + j < ti.cols) v[j] += __ldg(p.bias + ti.ocol + c0 + j);
+            }
+            if (r < ti.rows)
+              store_row(out + static_cast<size_t>(ti.orow + r) * p.ldo + ti.ocol + c0, v, vec_ok && c0 + 32 <= ti.cols,
+                        ti.cols - c0);
+          } else {
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+              uint4 u;
+              u.x = pack2(v[q * 8 + 0], v[q * 8 + 1], InT());
+              u.y = pack2(v[q * 8 + 2], v[q * 8 + 3], InT());
+              u.z = pack2(v[q * 8 + 4], v[q * 8 + 5], InT());
+              u.w = pack2(v[q * 8 + 6], v[q * 8 + 7], InT());
+              *reinterpret_cast<uint4*>(buf + (lane * 128 + (((c * 4 + q) ^ (lane & 15)) << 3)) * 2) = u;
+            }
+          }
+        }
+        if (!mine) {
+          fence_proxy_async();
+          __syncwarp();
+          if (lane == 0) {
+            InT* dst = reinterpret_cast<InT*>(p.stage[owner]) + (static_cast<size_t>(li) * p.sn + p.sme) * kTileElems;
+            bulk_store(dst + h * (kBM * 128) + quarter * 32 * 128, buf, kHalfSlabBytes);
+            bulk_commit_group();
+            bulk_wait_group_1();                               // everything but the copy just issued has completed
+            if (pend >= 0) mailbox_put(&mailbox, quarter, mb_tail, 0, pend);
+            pend = ((li * p.sn + owner) << 3) | (quarter << 1) | h;
+          }
+        }
+      }
+      if (failed) break;
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&tempty_bar[acc]);
+    }
+    if (failed) *abort_flag = 1;
+    if (lane == 0) {
+      bulk_wait_group0();
+      if (pend >= 0) mailbox_put(&mailbox, quarter, mb_tail, 0, pend);
+      __threadfence_block();
+      atomicAdd(const_cast<int*>(&mailbox.finished), 1);
+    }
+  }
+
+  if (*abort_flag) {
+    for (int i = 0; i < 64; ++i) __nanosleep(1000);
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, Cfg::kTmemCols);
+  }
+}
+
+template <bool AK, bool BK_, typename InT, bool F32>
+static void launch_ggs(const CUtensorMap& ta, const CUtensorMap& tb, const GgsParams& p, cudaStream_t stream) {
+  auto kern = gather_gemm_scatter_kernel<AK, BK_, InT, F32>;
+  static bool configured = false;
+  if (!configured) {
+    C10_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kFusedSmemBytes));
+    configured = true;
+  }
+  kern<<<p.num_gemm_ctas + p.num_comm_ctas, kGemmThreads, kFusedSmemBytes, stream>>>(ta, tb, p);
+  C10_CUDA_KERNEL_LAUNCH_CHECK();
+}
+
+template <typename InT, bool F32>
+static void dispatch_ggs(bool ak, bool bk, const CUtensorMap& ta, const CUtensorMap& tb, const GgsParams& p,
+                         cudaStream_t stream) {
+  if (ak && bk) launch_ggs<true, true, InT, F32>(ta, tb, p, stream);
+  else if (ak && !bk) launch_ggs<true, false, InT, F32>(ta, tb, p, stream);
+  else if (!ak && bk) launch_ggs<false, true, InT, F32>(ta, tb, p, stream);
+  else launch_ggs<false, false, InT, F32>(ta, tb, p, stream);
+}
+
+// One operand's gather, as the host describes it: cfg = [] (not gathered) or [n, me, g, panel_rows, epoch];
+// bufs / flags = every rank's gather buffer (this call's half) and flag array, indexed by group rank.
+static void fill_gather(const torch::Tensor& t, const std::vector<int64_t>& cfg, const std::vector<int64_t>& bufs,
+                        const std::vector<int64_t>& flags, GatherView& v, GatherPush& q) {
+  v = GatherView{};
+  q = GatherPush{};
+  if (cfg.empty()) return;
+  TORCH_CHECK(cfg.size() == 5 && bufs.size() == static_cast<size_t>(cfg[0]) && flags.size() == bufs.size());
+  const int n = static_cast<int>(cfg[0]), me = static_cast<int>(cfg[1]);
+  TORCH_CHECK(n >= 2 && n <= kMaxRanks && me >= 0 && me < n);
+  v.live = 1; v.n = n; v.g = static_cast<int>(cfg[2]);
+  v.R = static_cast<int>(t.size(0)); v.C = static_cast<int>(t.size(1));
+  v.panel_rows = static_cast<int>(cfg[3]);
+  v.panels = (v.R + v.panel_rows - 1) / v.panel_rows;
+  v.epoch = static_cast<int>(cfg[4]);
+  v.flags = reinterpret_cast<const int*>(flags[me]);
+  TORCH_CHECK(v.C % 8 == 0 && n * v.panels <= kKnownWords * 32, "gathered operand: bad shard shape or too many panels");
+  TORCH_CHECK(v.g == 0 || v.C % 64 == 0, "column-wise gather needs shard columns in multiples of 64");
+  q.live = 1; q.n = n; q.me = me; q.panels = v.panels; q.epoch = v.epoch;
+  q.shard_bytes = static_cast<long long>(v.R) * v.C * 2;
+  q.panel_bytes = static_cast<long long>(v.panel_rows) * v.C * 2;
+  q.src = reinterpret_cast<const uint8_t*>(t.data_ptr());
+  TORCH_CHECK((reinterpret_cast<uintptr_t>(q.src) & 15) == 0, "gathered operand must be 16-byte aligned");
+  for (int i = 0; i < n; ++i) {
+    q.dst[i] = reinterpret_cast<uint8_t*>(bufs[i]);
+    q.flags[i] = reinterpret_cast<int*>(flags[i]);
+  }
+}
+
+// out = reduce-scatter( op(gather(a)) op(gather(b)) ) + bias; see the head of this file.  `a`, `b` are this rank's
+// stored shards; `out` is pre-allocated with the shape of this rank's part of the product (fp32 or the input type).
+// sc = [] or [dim, n, me, epoch] with every rank's staging buffer (this call's half) and flag array.
+static void gather_gemm_scatter(torch::Tensor a, torch::Tensor b, bool trans_a, bool trans_b,
+                                c10::optional<torch::Tensor> bias, torch::Tensor out, std::vector<int64_t> ga,
+                                std::vector<int64_t> ga_bufs, std::vector<int64_t> ga_flags, std::vector<int64_t> gb,
+                                std::vector<int64_t> gb_bufs, std::vector<int64_t> gb_flags, std::vector<int64_t> sc,
+                                std::vector<int64_t> sc_stage, std::vector<int64_t> sc_flags, int64_t num_comm_ctas,
+                                int64_t status_ptr) {
+  TORCH_CHECK(a.is_cuda() && b.is_cuda() && a.dim() == 2 && b.dim() == 2 && a.is_contiguous() && b.is_contiguous());
+  TORCH_CHECK(a.scalar_type() == b.scalar_type() && out.is_contiguous() && out.dim() == 2);
+  TORCH_CHECK(a.scalar_type() == torch::kBFloat16 || a.scalar_type() == torch::kFloat16);
+  const bool f32 = out.scalar_type() == torch::kFloat32;
+  TORCH_CHECK(f32 || out.scalar_type() == a.scalar_type());
+  c10::cuda::CUDAGuard guard(a.device());
+  GgsParams p{};
+  fill_gather(a, ga, ga_bufs, ga_flags, p.va, p.pa);
+  fill_gather(b, gb, gb_bufs, gb_flags, p.vb, p.pb);
+  // full stored extents
+  const int64_t a_rows = a.size(0) * (p.va.live && p.va.g == 0 ? p.va.n : 1);
+  const int64_t a_cols = a.size(1) * (p.va.live && p.va.g == 1 ? p.va.n : 1);
+  const int64_t b_rows = b.size(0) * (p.vb.live && p.vb.g == 0 ? p.vb.n : 1);
+  const int64_t b_cols = b.size(1) * (p.vb.live && p.vb.g == 1 ? p.vb.n : 1);
+  const int M = static_cast<int>(trans_a ? a_cols : a_rows);
+  const int K = static_cast<int>(trans_a ? a_rows : a_cols);
+  const int N = static_cast<int>(trans_b ? b_rows : b_cols);
+  TORCH_CHECK((trans_b ? b_cols : b_rows) == K, "inner dimensions differ");
+  const bool ak = !trans_a, bk = trans_b;
+  // a gathered operand whose rows are the K dimension is concatenated without padding: K blocks may straddle
+  // sources only when the concatenation is along the rows (it is then contiguous); a column-wise concatenation of
+  // an MN-major operand would read the next source's rows past the end of K
+  if (p.va.live && p.va.g == 1 && !ak) TORCH_CHECK(p.va.R % kBK == 0, "A: K rows of a column-gathered operand must be a multiple of 64");
+  if (p.vb.live && p.vb.g == 1 && !bk) TORCH_CHECK(p.vb.R % kBK == 0, "B: K rows of a column-gathered operand must be a multiple of 64");
+  p.M = M; p.N = N; p.K = K;
+  p.is_bf16 = a.scalar_type() == torch::kBFloat16;
+  p.mn_lbo = 8192; p.mn_sbo = 1024;
+  p.sc_dim = -1; p.sn = 1; p.sme = 0; p.Ms = M; p.Ns = N;
+  if (!sc.empty()) {
+    TORCH_CHECK(sc.size() == 4 && sc_stage.size() == static_cast<size_t>(sc[1]) && sc_flags.size() == sc_stage.size());
+    p.sc_dim = static_cast<int>(sc[0]); p.sn = static_cast<int>(sc[1]); p.sme = static_cast<int>(sc[2]);
+    p.sepoch = static_cast<int>(sc[3]);
+    TORCH_CHECK(p.sn >= 2 && p.sn <= kMaxRanks && (p.sc_dim == 0 || p.sc_dim == 1));
+    if (p.sc_dim == 0) { TORCH_CHECK(M % p.sn == 0); p.Ms = M / p.sn; }
+    else { TORCH_CHECK(N % p.sn == 0 && (N / p.sn) % 8 == 0); p.Ns = N / p.sn; }
+    for (int i = 0; i < p.sn; ++i) {
+      p.stage[i] = reinterpret_cast<void*>(sc_stage[i]);
+      p.sflags[i] = reinterpret_cast<int*>(sc_flags[i]);
+    }
+    // boxes of a column-gathered MN-major operand must stay inside one source for every owner's tiles
+    if (p.sc_dim == 0 && !ak) TORCH_CHECK(p.Ms % 8 == 0, "row shards of an MN-major A must start on 16-byte boundaries");
+    if (p.sc_dim == 0 && p.va.live && p.va.g == 1 && !ak) TORCH_CHECK(p.Ms % 64 == 0);
+    if (p.sc_dim == 1 && p.vb.live && p.vb.g == 1 && bk == false) TORCH_CHECK(p.Ns % 64 == 0);
+  }
+  TORCH_CHECK(out.size(0) == p.Ms && out.size(1) == p.Ns, "output must have the shape of this rank's part");
+  p.tiles_m = (p.Ms + kBM - 1) / kBM;
+  p.tiles_n = (p.Ns + kFusedBN - 1) / kFusedBN;
+  p.out = out.data_ptr();
+  p.ldo = static_cast<int>(out.size(1));
+  torch::Tensor bias_f;
+  if (bias.has_value() && bias->defined()) {
+    bias_f = bias->to(torch::kFloat32).contiguous();
+    TORCH_CHECK(bias_f.numel() == p.Ns);
+    p.bias = bias_f.data_ptr<float>();
+  }
+  p.status = reinterpret_cast<int*>(status_ptr);
+  // start the K loop at the local shard when K is the gathered dimension
+  const int kb_total = (K + kBK - 1) / kBK;
+  p.k_start = 0;
+  if (p.va.live && ((ak && p.va.g == 1) || (!ak && p.va.g == 0)))
+    p.k_start = static_cast<int>(static_cast<int64_t>(p.pa.me) * (K / p.va.n) / kBK);
+  else if (p.vb.live && ((bk && p.vb.g == 1) || (!bk && p.vb.g == 0)))
+    p.k_start = static_cast<int>(static_cast<int64_t>(p.pb.me) * (K / p.vb.n) / kBK);
+  p.k_start = std::min(p.k_start, kb_total - 1);
+  p.b_first = (p.pb.live && (!p.pa.live || p.pb.shard_bytes < p.pa.shard_bytes)) ? 1 : 0;
+  const int sms = at::cuda::getCurrentDeviceProperties()->multiProcessorCount;
+  p.num_comm_ctas = (p.pa.live || p.pb.live) ? std::max(1, std::min(static_cast<int>(num_comm_ctas), sms / 2)) : 0;
+  p.num_gemm_ctas = sms - p.num_comm_ctas;
+  TORCH_CHECK(p.num_gemm_ctas >= 2);
+
+  const void* a_ptr = p.va.live ? reinterpret_cast<const void*>(ga_bufs[p.pa.me]) : a.data_ptr();
+  const void* b_ptr = p.vb.live ? reinterpret_cast<const void*>(gb_bufs[p.pb.me]) : b.data_ptr();
+  const uint64_t ar = p.va.live ? static_cast<uint64_t>(p.va.n) * a.size(0) : a.size(0);
+  const uint64_t br = p.vb.live ? static_cast<uint64_t>(p.vb.n) * b.size(0) : b.size(0);
+  CUtensorMap ta = make_tma_2d(a_ptr, ar, a.size(1), a.size(1), ak ? kBM : 64);
+  CUtensorMap tb = make_tma_2d(b_ptr, br, b.size(1), b.size(1), bk ? kFusedBN : 64);
+  auto stream = at::cuda::getCurrentCUDAStream();
+  if (p.is_bf16) {
+    if (f32) dispatch_ggs<__nv_bfloat16, true>(ak, bk, ta, tb, p, stream);
+    else dispatch_ggs<__nv_bfloat16, false>(ak, bk, ta, tb, p, stream);
+  } else {
+    if (f32) dispatch_ggs<__half, true>(ak, bk, ta, tb, p, stream);
+    else dispatch_ggs<__half, false>(ak, bk, ta, tb, p, stream);
+  }
+}
+
+void register_ggs(py::module& m) { m.def("gather_gemm_scatter", &gather_gemm_scatter); }
+
+}  // namespace cw

@@ -36,6 +36,19 @@ def prefer_fused(M, N, K, n) -> bool:
     return t_gemm >= 1.5 * t_link
 
 
+def prefer_fused_gather_scatter(M, N, K) -> bool:
+    """The gather / reduce-scatter fused kernel is used for products large enough that the exchange can hide
+    behind them (tens of microseconds of tensor-core time); tiny products are launch-latency bound either way."""
+    if _DISABLED:
+        return False
+    if _POLICY == "1":
+        return True
+    return 2.0 * M * N * K >= _GGS_MIN_FLOPS
+
+
+_GGS_MIN_FLOPS = float(os.environ.get("CUBEWORK_B200_FUSED_MIN_GFLOP", "20")) * 1e9
+
+
 def available() -> bool:
     if _DISABLED or not torch.cuda.is_available():
         return False

@@ -58,6 +58,66 @@ def _check_fused_all_reduce():
         assert all(torch.equal(g, gathered[0]) for g in gathered), "ranks disagree on the reduced result"
 
 
+def _check_gather_gemm_scatter():
+    """Every operand-gather / output-scatter pattern of the 2D and 3D products, all over one 2-rank group,
+    against an fp32 product of the gathered operands (torch collectives + matmul)."""
+    import torch.distributed as dist
+
+    from cubework_b200.distributed import ParallelManager as pm
+    from cubework_b200.ops import ext
+    from cubework_b200.parallel import fused, symm, symm_impl
+    assert symm.available()
+    symm._POLICY = "1"
+    mode = pm.PARALLEL_1D
+    n, r = mode.world_size, mode.local_rank
+    dev = torch.device("cuda", torch.cuda.current_device())
+    torch.manual_seed(0)
+    f32 = torch.float32
+    # (M, N, K, trans_a, trans_b, gather_a dim, gather_b dim, scatter dim, out dtype, bias)
+    cases = [
+        (1000, 520, 384, False, False, 1, 0, None, None, False),      # SUMMA AB: both operands gathered along K
+        (1000, 528, 200, False, True, None, 0, 1, None, False),       # SUMMA ABT: B gathered along N, scatter N
+        (640, 520, 448, True, False, 1, None, 0, f32, False),         # SUMMA ATB: A^T gathered along M, scatter M
+        (1000, 520, 264, False, True, 0, 0, 0, None, True),           # 3D forward, weight [out, in]
+        (1000, 640, 320, False, False, 0, 1, 0, None, True),          # 3D forward, weight [in, out]
+        (1024, 520, 328, False, False, None, None, 0, None, False),   # 3D dX: scatter only
+        (528, 400, 1000, True, False, None, None, 1, f32, False),     # 3D dW: scatter columns, fp32
+        (8192, 2048, 1024, False, True, 0, None, 1, None, False),     # many panels, more tiles than CTAs
+        (4096, 4096, 2048, False, False, 1, 0, None, None, False),
+    ]
+    for (M, N, K, ta, tb, ga, gb, sc, odt, with_bias) in cases:
+        a_full = torch.randn((K, M) if ta else (M, K), device=dev).bfloat16()
+        b_full = torch.randn((N, K) if tb else (K, N), device=dev).bfloat16()
+        for t in (a_full, b_full):
+            dist.broadcast(t, src=0)
+        # each rank contributes 1/n of the sum when nothing is scattered... the product is the same on all ranks,
+        # so a scattered result is n x the plain product
+        a = a_full if ga is None else a_full.chunk(n, dim=ga)[r].contiguous()
+        b = b_full if gb is None else b_full.chunk(n, dim=gb)[r].contiguous()
+        ref = (a_full.float().t() if ta else a_full.float()) @ (b_full.float().t() if tb else b_full.float())
+        if sc is not None:
+            ref = (ref * n).chunk(n, dim=sc)[r]
+        bias = None
+        if with_bias:
+            bias = torch.randn(ref.shape[1], device=dev)
+            ref = ref + bias
+        kw = dict(gather_a=None if ga is None else (mode, ga), gather_b=None if gb is None else (mode, gb),
+                  scatter=None if sc is None else (mode, sc), bias=bias, out_dtype=odt)
+        before = symm_impl.STATS["gather_gemm_scatter"]
+        for rep in range(3):        # both halves of the buffers, growing epochs
+            out, a_g, b_g = fused.gather_gemm_reduce(a, b, ta, tb, keep_gathered=True, **kw)
+            torch.cuda.synchronize()
+            ext.check_status()
+            assert out.dtype == (odt or a.dtype) and out.shape == ref.shape
+            assert _rel(out, ref) < 8e-3, (M, N, K, ta, tb, ga, gb, sc, rep, _rel(out, ref))
+            assert torch.equal(a_g, a_full) and torch.equal(b_g, b_full)
+        assert symm_impl.STATS["gather_gemm_scatter"] - before == 3, "the fused kernel did not run for this pattern"
+
+
+def test_fused_gather_gemm_scatter_two_ranks():
+    _multi(_check_gather_gemm_scatter, 2)
+
+
 def _check_layers_bf16():
     import torch.distributed as dist
     import torch.nn.functional as F
