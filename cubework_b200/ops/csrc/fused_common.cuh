@@ -57,6 +57,11 @@ __device__ __forceinline__ bool wait_flag(const int* flag, int epoch, int* statu
   }
 }
 
+// Fused kernels run the six warps of the plain GEMM plus one publisher warp: the thread that publishes flags sits
+// in system-scope fences for tens of microseconds at a time and must not share a warp with the TMA producer or
+// the MMA issuer, whose instruction issue it would hold up.
+constexpr int kFusedThreads = kGemmThreads + 32;
+constexpr int kPublisherWarp = kGemmThreads / 32;
 constexpr int kFusedStages = 4;
 constexpr int kSlabBytes = 32 * kFusedBN * 2;                 // one epilogue warp's 32 rows of a tile (16 KB)
 constexpr int kEpiBytes = 4 * 32 * 128 * 2;                    // 32 KB: one 32 x 128 half-slab per epilogue warp
@@ -97,7 +102,7 @@ constexpr int kHalfSlabBytes = 32 * 128 * 2;                   // 8 KB: one warp
 // ---- flag publication -------------------------------------------------------------------------------------
 // A system-scope release towards another GPU costs tens of microseconds while the links are busy, far too much to
 // pay on the epilogue's critical path once per copy.  Epilogue warps therefore only *record* completed copies in a
-// per-warp mailbox in shared memory; one otherwise idle thread of the CTA (lane 1 of the producer warp) collects
+// per-warp mailbox in shared memory; one thread of a warp of its own collects
 // whatever has accumulated, issues ONE system-scope fence and then writes all the corresponding flags.
 constexpr int kMailboxDepth = 16;
 struct Mailbox {

@@ -57,7 +57,7 @@ __device__ __forceinline__ int push_item_tile(int p, int n, int me, int num_tile
 }
 
 template <bool A_KMAJOR, bool B_KMAJOR, typename InT>
-__global__ void __launch_bounds__(kGemmThreads, 1)
+__global__ void __launch_bounds__(kFusedThreads, 1)
 gemm_allreduce_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
                       const __grid_constant__ CUtensorMap tma_out, FusedParams p) {
   constexpr int BN = kFusedBN;
@@ -232,7 +232,46 @@ gemm_allreduce_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_co
           if (++stage == kFusedStages) { stage = 0; phase ^= 1; }
         }
       }
-    } else if (lane == 1) {
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      const uint32_t idesc = make_idesc_f16(kBM, BN, !A_KMAJOR, !B_KMAJOR, p.is_bf16);
+      int stage = 0;
+      uint32_t phase = 0;
+      int it = 0;
+      for (int k = 0; !*abort_flag; ++k) {
+        const int t = tile_of(k);
+        if (t == -2) break;
+        if (t < 0) continue;
+        const int acc = it & 1;
+        const uint32_t acc_phase = (it >> 1) & 1;
+        ++it;
+        if (!mbar_wait(&tempty_bar[acc], acc_phase ^ 1, abort_flag, p.status, kErrTmemEmptyTimeout, t)) break;
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + acc * BN;
+        bool ok = true;
+        for (int kb = 0; kb < kb_total; ++kb) {
+          if (!mbar_wait(&full_bar[stage], phase, abort_flag, p.status, kErrFullBarrierTimeout, t)) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t sa = smem_u32(smem + stage * Cfg::kStageBytes);
+          const uint32_t sb = sa + Cfg::kABytes;
+#pragma unroll
+          for (int k16 = 0; k16 < kBK / 16; ++k16) {
+            const uint64_t da = A_KMAJOR ? make_smem_desc(sa + k16 * 32, 16, 1024)
+                                         : make_smem_desc(sa + k16 * 2048, p.mn_lbo, p.mn_sbo);
+            const uint64_t db = B_KMAJOR ? make_smem_desc(sb + k16 * 32, 16, 1024)
+                                         : make_smem_desc(sb + k16 * 2048, p.mn_lbo, p.mn_sbo);
+            tc_mma_f16(d_tmem, da, db, idesc, (kb > 0 || k16 > 0) ? 1u : 0u);
+          }
+          tc_commit(&empty_bar[stage]);
+          if (++stage == kFusedStages) { stage = 0; phase ^= 1; }
+        }
+        if (!ok) break;
+        tc_commit(&tfull_bar[acc]);
+      }
+    }
+  } else if (warp == kPublisherWarp) {
+    if (lane == 0) {
       // ---- publisher: batches completed copies, one system-scope fence per batch, then the flags
       int head[4] = {0, 0, 0, 0};
       const unsigned long long t_start = globaltimer_ns();
@@ -271,43 +310,6 @@ gemm_allreduce_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_co
             st_relaxed_sys(p.flags[owner] + p.done_cap * 8 + (static_cast<size_t>(li) * p.n + p.me) * 8 + qh, p.epoch);
           }
         }
-      }
-    }
-  } else if (warp == 1) {
-    if (lane == 0) {
-      const uint32_t idesc = make_idesc_f16(kBM, BN, !A_KMAJOR, !B_KMAJOR, p.is_bf16);
-      int stage = 0;
-      uint32_t phase = 0;
-      int it = 0;
-      for (int k = 0; !*abort_flag; ++k) {
-        const int t = tile_of(k);
-        if (t == -2) break;
-        if (t < 0) continue;
-        const int acc = it & 1;
-        const uint32_t acc_phase = (it >> 1) & 1;
-        ++it;
-        if (!mbar_wait(&tempty_bar[acc], acc_phase ^ 1, abort_flag, p.status, kErrTmemEmptyTimeout, t)) break;
-        tc_fence_after();
-        const uint32_t d_tmem = tmem_base + acc * BN;
-        bool ok = true;
-        for (int kb = 0; kb < kb_total; ++kb) {
-          if (!mbar_wait(&full_bar[stage], phase, abort_flag, p.status, kErrFullBarrierTimeout, t)) { ok = false; break; }
-          tc_fence_after();
-          const uint32_t sa = smem_u32(smem + stage * Cfg::kStageBytes);
-          const uint32_t sb = sa + Cfg::kABytes;
-#pragma unroll
-          for (int k16 = 0; k16 < kBK / 16; ++k16) {
-            const uint64_t da = A_KMAJOR ? make_smem_desc(sa + k16 * 32, 16, 1024)
-                                         : make_smem_desc(sa + k16 * 2048, p.mn_lbo, p.mn_sbo);
-            const uint64_t db = B_KMAJOR ? make_smem_desc(sb + k16 * 32, 16, 1024)
-                                         : make_smem_desc(sb + k16 * 2048, p.mn_lbo, p.mn_sbo);
-            tc_mma_f16(d_tmem, da, db, idesc, (kb > 0 || k16 > 0) ? 1u : 0u);
-          }
-          tc_commit(&empty_bar[stage]);
-          if (++stage == kFusedStages) { stage = 0; phase ^= 1; }
-        }
-        if (!ok) break;
-        tc_commit(&tfull_bar[acc]);
       }
     }
   } else {
@@ -467,7 +469,7 @@ static void launch_fused(const CUtensorMap& ta, const CUtensorMap& tb, const CUt
     C10_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kFusedSmemBytes));
     configured = true;
   }
-  kern<<<p.num_gemm_ctas + p.num_comm_ctas, kGemmThreads, kFusedSmemBytes, stream>>>(ta, tb, tout, p);
+  kern<<<p.num_gemm_ctas + p.num_comm_ctas, kFusedThreads, kFusedSmemBytes, stream>>>(ta, tb, tout, p);
   C10_CUDA_KERNEL_LAUNCH_CHECK();
 }
 

@@ -9,13 +9,14 @@
 //
 // Grid = C communication CTAs + G GEMM CTAs, all co-resident (one CTA per SM).
 //  * communication CTAs push this rank's shard, panel by panel (a panel = a block of stored rows), into the
-//    gather buffer of every rank of the operand's group (its own included) with bulk copies
-//    global -> shared -> peer, and publish one arrival flag per (destination, panel).  They wait for nobody.
+//    gather buffer of every other rank of the operand's group with bulk copies global -> shared -> peer, and
+//    publish one arrival flag per (destination, panel).  They wait for nobody.  The own shard is read in place
+//    by the GEMM CTAs (it is copied into the own buffer only when TMA boxes could straddle two sources).
 //  * GEMM CTAs run the persistent TMA -> tcgen05 -> TMEM pipeline.  The TMA producer reads a gathered
-//    operand from the *local* gather buffer [sources][rows][cols]; before the first load that touches a
-//    (source, panel) it waits for that panel's flag (remembered in a shared-memory bitmap afterwards).  The
-//    K loop starts at the k-blocks of the local shard, so multiplication begins while remote panels are
-//    still in flight.
+//    operand from the *local* gather buffer [sources][rows][cols]; before the first load of a tile it waits
+//    for the flags of the (source, panel) pairs the tile reads (remembered in a shared-memory bitmap
+//    afterwards), so tiles whose operands are local start at once.  The K loop starts at the k-blocks of the
+//    local shard.
 //  * with a reduce-scatter, tile ownership follows the output shard: "push" CTAs compute tiles of other
 //    owners and send the 16-bit partials into the owner's staging buffer (8 KB bulk copies, flags batched
 //    behind one system-scope fence by a publisher thread); "own" CTAs compute this rank's tiles, wait for
@@ -53,11 +54,14 @@ struct GatherView {          // how the TMA producer sees one operand
   int R, C;                  // extent of one stored shard
   int panel_rows, panels;    // one arrival flag per `panel_rows` stored rows of a source
   int epoch;
+  int me;                    // this rank's position among the sources
+  int own_direct;            // this rank's own shard is read from the tensor itself, not from the gather buffer
   const int* flags;          // local [n][panels]
 };
 
 struct GatherPush {          // what the communication CTAs do for one operand
   int live, n, me, panels, epoch;
+  int dests;                 // destinations per panel: n, or n - 1 when the own shard is read in place
   long long shard_bytes, panel_bytes;
   const uint8_t* src;        // this rank's shard, dense [R][C] 16-bit
   uint8_t* dst[kMaxRanks];   // every rank's gather buffer (own included): [n][R][C]
@@ -116,8 +120,16 @@ __device__ __forceinline__ TileInfo tile_info(const GgsParams& p, int owner, int
   return t;
 }
 
+// The producer thread's record of what has arrived: one bit per (source, panel) in shared memory, and their count.
+struct Known {
+  uint32_t* bits;
+  int count, total;
+  __device__ __forceinline__ bool all() const { return count >= total; }
+};
+
 // rows [r0, r1) of source s must have arrived
-__device__ __forceinline__ bool ensure_panels(const GatherView& v, uint32_t* known, int s, int r0, int r1, int* status) {
+__device__ __forceinline__ bool ensure_panels(const GatherView& v, Known& kn, int s, int r0, int r1, int* status) {
+  uint32_t* known = kn.bits;
   if (r1 <= r0) return true;
   for (int pnl = r0 / v.panel_rows; pnl <= (r1 - 1) / v.panel_rows; ++pnl) {
     const int idx = s * v.panels + pnl;
@@ -125,11 +137,12 @@ __device__ __forceinline__ bool ensure_panels(const GatherView& v, uint32_t* kno
     if (!wait_flag(v.flags + idx, v.epoch, status, idx)) return false;
     fence_proxy_async_all();                      // the TMA reads that follow must see what the flag announced
     known[idx >> 5] |= 1u << (idx & 31);
+    ++kn.count;
   }
   return true;
 }
 // rows [y0, y1) of the concatenation along the rows (g == 0)
-__device__ __forceinline__ bool ensure_stacked(const GatherView& v, uint32_t* known, int y0, int y1, int* status) {
+__device__ __forceinline__ bool ensure_stacked(const GatherView& v, Known& known, int y0, int y1, int* status) {
   y1 = min(y1, v.n * v.R);
   while (y0 < y1) {
     const int s = y0 / v.R, r = y0 - s * v.R;
@@ -140,23 +153,104 @@ __device__ __forceinline__ bool ensure_stacked(const GatherView& v, uint32_t* kn
   return true;
 }
 
-// Coordinates of one TMA box of an operand + the arrival check.  (x, y) = (column, row) of the box in the full
-// (gathered) stored operand, h = rows of the box.  Boxes are 64 columns wide and, along a column-wise
-// concatenation, never straddle two sources (the host checks the divisibility that guarantees it).
-__device__ __forceinline__ bool locate(const GatherView& v, uint32_t* known, int& x, int& y, int h, int* status) {
+// ---- what the TMA producer needs to know about one operand for one tile ---------------------------------------
+// All divisions happen once per tile; the k loop only adds and compares.  A box is 64 columns wide; along a
+// column-wise concatenation it never straddles two sources (the host checks the divisibility that guarantees it).
+//
+// Arrival is checked per tile, before its first load: every (source, panel) the tile will read must have landed.
+// (Tiles whose operands are entirely local therefore start at once; the others start when their panels are in.)
+template <bool KMAJOR, int BOXES>
+struct OperandTile {
+  int x[BOXES], ybase[BOXES];      // MN-major: column and row offset of box g (row = ybase + k)
+  bool local[BOXES];               // box g comes from this rank's own tensor
+  int s, xin;                      // K-major, column-wise concatenation: source and column of the current k block
+  int y;                           // K-major: row of the box (in the gather buffer, or in the own tensor if local[0])
+};
+
+__device__ __forceinline__ bool ensure_source(const GatherView& v, Known& known, int s, int r0, int r1, int* status) {
+  if (s >= v.n || (v.own_direct && s == v.me)) return true;
+  return ensure_panels(v, known, s, r0, r1, status);
+}
+
+// mn0 .. mn0 + len: the rows (A) or columns (B) of the product this tile covers
+template <bool KMAJOR, int BOXES>
+__device__ __forceinline__ bool begin_tile(const GatherView& v, Known& known, int mn0, int len, int kb_first,
+                                           OperandTile<KMAJOR, BOXES>& t, int* status) {
+  if (KMAJOR) {
+    t.y = mn0; t.local[0] = false; t.s = 0; t.xin = kb_first * kBK;
+    if (!v.live) return true;
+    if (v.g == 0) {                                          // rows of the concatenation = MN
+      if (v.own_direct && mn0 >= v.me * v.R && mn0 < (v.me + 1) * v.R) {
+        t.y = mn0 - v.me * v.R;
+        t.local[0] = true;
+        return true;
+      }
+      return known.all() || ensure_stacked(v, known, mn0, mn0 + len, status);
+    }
+    t.s = t.xin / v.C;                                       // K is concatenated: every source, these rows
+    t.xin -= t.s * v.C;
+    for (int s = 0; s < v.n && !known.all(); ++s)
+      if (!ensure_source(v, known, s, min(mn0, v.R), min(mn0 + len, v.R), status)) return false;
+    return true;
+  }
+#pragma unroll
+  for (int g = 0; g < BOXES; ++g) {
+    t.x[g] = mn0 + g * 64; t.ybase[g] = 0; t.local[g] = false;
+  }
   if (!v.live) return true;
-  if (v.g == 0) return ensure_stacked(v, known, y, y + h, status);
-  const int s = x / v.C;
-  if (s >= v.n) return true;                     // beyond the operand: the load is zero-filled
-  x -= s * v.C;
-  const bool ok = ensure_panels(v, known, s, min(y, v.R), min(y + h, v.R), status);
-  y += s * v.R;
-  return ok;
+  if (v.g == 0) {                                            // rows of the concatenation = K: everything is needed
+    for (int s = 0; s < v.n && !known.all(); ++s)
+      if (!ensure_source(v, known, s, 0, v.R, status)) return false;
+    return true;
+  }
+#pragma unroll
+  for (int g = 0; g < BOXES; ++g) {                          // MN is concatenated by columns: the sources of the boxes
+    const int s = t.x[g] / v.C;
+    if (s >= v.n) continue;                                  // beyond the operand: zero-filled
+    t.x[g] -= s * v.C;
+    if (v.own_direct && s == v.me) {
+      t.local[g] = true;
+    } else {
+      t.ybase[g] = s * v.R;
+      if (!known.all() && !ensure_panels(v, known, s, 0, v.R, status)) return false;
+    }
+  }
+  return true;
+}
+
+// Coordinates of box g for k block `kb`; `local` tells which tensor map to use.
+template <bool KMAJOR, int BOXES>
+__device__ __forceinline__ void box_at(const GatherView& v, const OperandTile<KMAJOR, BOXES>& t, int g, int kb, int& x,
+                                       int& y, bool& local) {
+  if (KMAJOR) {
+    x = kb * kBK; y = t.y; local = t.local[0];
+    if (v.live && v.g == 1) {
+      x = t.xin;
+      local = v.own_direct && t.s == v.me;
+      if (!local) y = t.s * v.R + t.y;
+    }
+    return;
+  }
+  x = t.x[g]; y = kb * kBK + t.ybase[g]; local = t.local[g];
+  if (v.live && v.g == 0 && v.own_direct && y >= v.me * v.R && y < (v.me + 1) * v.R) {
+    y -= v.me * v.R;
+    local = true;
+  }
+}
+
+// advance to the next k block (K-major operand whose K is concatenated: follow the source boundaries)
+template <bool KMAJOR, int BOXES>
+__device__ __forceinline__ void next_kb(const GatherView& v, OperandTile<KMAJOR, BOXES>& t, bool wrapped) {
+  if (!KMAJOR || !v.live || v.g != 1) return;
+  if (wrapped) { t.s = 0; t.xin = 0; return; }
+  t.xin += kBK;
+  if (t.xin >= v.C) { t.xin = 0; ++t.s; }
 }
 
 template <bool A_KMAJOR, bool B_KMAJOR, typename InT, bool OUT_F32>
-__global__ void __launch_bounds__(kGemmThreads, 1)
+__global__ void __launch_bounds__(kFusedThreads, 1)
 gather_gemm_scatter_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
+                           const __grid_constant__ CUtensorMap tma_a_own, const __grid_constant__ CUtensorMap tma_b_own,
                            const __grid_constant__ GgsParams p) {
   constexpr int BN = kFusedBN;
   using Cfg = GemmCfg<BN>;
@@ -191,8 +285,8 @@ gather_gemm_scatter_kernel(const __grid_constant__ CUtensorMap tma_a, const __gr
     const int c = blockIdx.x;
     const GatherPush& first = p.b_first ? p.pb : p.pa;
     const GatherPush& second = p.b_first ? p.pa : p.pb;
-    const int n_first = first.live ? first.panels * first.n : 0;
-    const int n_second = second.live ? second.panels * second.n : 0;
+    const int n_first = first.live ? first.panels * first.dests : 0;
+    const int n_second = second.live ? second.panels * second.dests : 0;
 
     if (warp == 2) {
       // ---- publisher
@@ -231,8 +325,8 @@ gather_gemm_scatter_kernel(const __grid_constant__ CUtensorMap tma_a, const __gr
       const bool is_second = i >= n_first;
       const GatherPush& op = is_second ? second : first;
       const int idx = is_second ? i - n_first : i;
-      const int panel = idx / op.n;
-      const int dest = (op.me + idx % op.n) % op.n;
+      const int panel = idx / op.dests;
+      const int dest = (op.me + (op.n - op.dests) + idx % op.dests) % op.n;
       const long long off0 = static_cast<long long>(panel) * op.panel_bytes;
       const long long bytes = min(op.panel_bytes, op.shard_bytes - off0);
       const uint8_t* src = op.src + off0;
@@ -298,6 +392,8 @@ gather_gemm_scatter_kernel(const __grid_constant__ CUtensorMap tma_a, const __gr
     fence_barrier_init();
     tma_prefetch_desc(&tma_a);
     tma_prefetch_desc(&tma_b);
+    tma_prefetch_desc(&tma_a_own);
+    tma_prefetch_desc(&tma_b_own);
   }
   if (threadIdx.x >= 32 && threadIdx.x < 32 + kKnownWords) {
     known_a[threadIdx.x - 32] = 0;
@@ -341,88 +437,40 @@ gather_gemm_scatter_kernel(const __grid_constant__ CUtensorMap tma_a, const __gr
       int stage = 0;
       uint32_t phase = 0;
       int owner, li;
+      Known ka{known_a, 0, p.va.live ? (p.va.n - p.va.own_direct) * p.va.panels : 0};
+      Known kb_{known_b, 0, p.vb.live ? (p.vb.n - p.vb.own_direct) * p.vb.panels : 0};
       for (int k = 0; !*abort_flag && tile_of(k, owner, li); ++k) {
         const TileInfo ti = tile_info(p, owner, li, kb_total);
-        bool ok = true;
-        for (int kbi = 0; kbi < kb_total && ok; ++kbi) {
-          int kb = kbi + p.k_start;
-          if (kb >= kb_total) kb -= kb_total;
+        OperandTile<A_KMAJOR, kBM / 64> ta;
+        OperandTile<B_KMAJOR, BN / 64> tb;
+        bool ok = begin_tile(p.va, ka, ti.row0, kBM, p.k_start, ta, p.status) &&
+                  begin_tile(p.vb, kb_, ti.col0, BN, p.k_start, tb, p.status);
+        if (!ok) { *abort_flag = 1; break; }
+        int kb = p.k_start;
+        for (int kbi = 0; kbi < kb_total; ++kbi) {
           if (!mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag, p.status, kErrEmptyBarrierTimeout, li)) { ok = false; break; }
           uint8_t* sa = smem + stage * Cfg::kStageBytes;
           uint8_t* sb = sa + Cfg::kABytes;
-          int ax[2], ay[2], bx[4], by[4];
-          if (A_KMAJOR) {
-            ax[0] = kb * kBK; ay[0] = ti.row0;
-            ok = ok && locate(p.va, known_a, ax[0], ay[0], kBM, p.status);
-          } else {
-#pragma unroll
-            for (int g = 0; g < kBM / 64; ++g) {
-              ax[g] = ti.row0 + g * 64; ay[g] = kb * kBK;
-              ok = ok && locate(p.va, known_a, ax[g], ay[g], kBK, p.status);
-            }
-          }
-          if (B_KMAJOR) {
-            bx[0] = kb * kBK; by[0] = ti.col0;
-            ok = ok && locate(p.vb, known_b, bx[0], by[0], BN, p.status);
-          } else {
-#pragma unroll
-            for (int g = 0; g < BN / 64; ++g) {
-              bx[g] = ti.col0 + g * 64; by[g] = kb * kBK;
-              ok = ok && locate(p.vb, known_b, bx[g], by[g], kBK, p.status);
-            }
-          }
-          if (!ok) { *abort_flag = 1; break; }
           mbar_expect_tx(&full_bar[stage], Cfg::kStageBytes);
-          if (A_KMAJOR) {
-            tma_load_2d(sa, &tma_a, &full_bar[stage], ax[0], ay[0]);
-          } else {
+          int x, y;
+          bool local;
 #pragma unroll
-            for (int g = 0; g < kBM / 64; ++g) tma_load_2d(sa + g * 8192, &tma_a, &full_bar[stage], ax[g], ay[g]);
+          for (int g = 0; g < (A_KMAJOR ? 1 : kBM / 64); ++g) {
+            box_at(p.va, ta, g, kb, x, y, local);
+            tma_load_2d(sa + g * 8192, local ? &tma_a_own : &tma_a, &full_bar[stage], x, y);
           }
-          if (B_KMAJOR) {
-            tma_load_2d(sb, &tma_b, &full_bar[stage], bx[0], by[0]);
-          } else {
 #pragma unroll
-            for (int g = 0; g < BN / 64; ++g) tma_load_2d(sb + g * 8192, &tma_b, &full_bar[stage], bx[g], by[g]);
+          for (int g = 0; g < (B_KMAJOR ? 1 : BN / 64); ++g) {
+            box_at(p.vb, tb, g, kb, x, y, local);
+            tma_load_2d(sb + g * 8192, local ? &tma_b_own : &tma_b, &full_bar[stage], x, y);
           }
+          const bool wrapped = ++kb == kb_total;
+          if (wrapped) kb = 0;
+          next_kb(p.va, ta, wrapped);
+          next_kb(p.vb, tb, wrapped);
           if (++stage == kFusedStages) { stage = 0; phase ^= 1; }
         }
         if (!ok) break;
-      }
-    } else if (lane == 1 && scat) {
-      // ---- publisher of the partial tiles this CTA pushed: one system-scope fence per batch, then the flags
-      int head[4] = {0, 0, 0, 0};
-      const unsigned long long t_start = globaltimer_ns();
-      for (;;) {
-        int batch[32];
-        int nb = 0;
-        const int fin = mailbox.finished;
-        for (int q = 0; q < 4; ++q) {
-          const int tail = mailbox.tail[q];
-          while (head[q] < tail && nb < 32) {
-            batch[nb++] = mailbox.item[q][head[q] % kMailboxDepth];
-            ++head[q];
-          }
-          mailbox.head[q] = head[q];
-        }
-        if (nb == 0) {
-          if (fin == 4 || *abort_flag) {
-            bool drained = true;
-            for (int q = 0; q < 4; ++q) drained = drained && head[q] == mailbox.tail[q];
-            if (drained) break;
-            continue;
-          }
-          if (globaltimer_ns() - t_start > 4 * kWaitLimitNs) break;
-          __nanosleep(100);
-          continue;
-        }
-        __threadfence_block();
-        __threadfence_system();
-        for (int b = 0; b < nb; ++b) {
-          const int slot_id = batch[b] >> 3, qh = batch[b] & 7;
-          const int owner = slot_id % p.sn, li = slot_id / p.sn;
-          st_relaxed_sys(p.sflags[owner] + (static_cast<size_t>(li) * p.sn + p.sme) * 8 + qh, p.sepoch);
-        }
       }
     }
   } else if (warp == 1) {
@@ -458,6 +506,43 @@ gather_gemm_scatter_kernel(const __grid_constant__ CUtensorMap tma_a, const __gr
         }
         if (!ok) break;
         tc_commit(&tfull_bar[acc]);
+      }
+    }
+  } else if (warp == kPublisherWarp) {
+    if (lane == 0 && scat) {
+      // ---- publisher of the partial tiles this CTA pushed: one system-scope fence per batch, then the flags
+      int head[4] = {0, 0, 0, 0};
+      const unsigned long long t_start = globaltimer_ns();
+      for (;;) {
+        int batch[32];
+        int nb = 0;
+        const int fin = mailbox.finished;
+        for (int q = 0; q < 4; ++q) {
+          const int tail = mailbox.tail[q];
+          while (head[q] < tail && nb < 32) {
+            batch[nb++] = mailbox.item[q][head[q] % kMailboxDepth];
+            ++head[q];
+          }
+          mailbox.head[q] = head[q];
+        }
+        if (nb == 0) {
+          if (fin == 4 || *abort_flag) {
+            bool drained = true;
+            for (int q = 0; q < 4; ++q) drained = drained && head[q] == mailbox.tail[q];
+            if (drained) break;
+            continue;
+          }
+          if (globaltimer_ns() - t_start > 4 * kWaitLimitNs) break;
+          __nanosleep(100);
+          continue;
+        }
+        __threadfence_block();
+        __threadfence_system();
+        for (int b = 0; b < nb; ++b) {
+          const int slot_id = batch[b] >> 3, qh = batch[b] & 7;
+          const int owner = slot_id % p.sn, li = slot_id / p.sn;
+          st_relaxed_sys(p.sflags[owner] + (static_cast<size_t>(li) * p.sn + p.sme) * 8 + qh, p.sepoch);
+        }
       }
     }
   } else {
@@ -580,24 +665,25 @@ gather_gemm_scatter_kernel(const __grid_constant__ CUtensorMap tma_a, const __gr
 }
 
 template <bool AK, bool BK_, typename InT, bool F32>
-static void launch_ggs(const CUtensorMap& ta, const CUtensorMap& tb, const GgsParams& p, cudaStream_t stream) {
+static void launch_ggs(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tao, const CUtensorMap& tbo,
+                       const GgsParams& p, cudaStream_t stream) {
   auto kern = gather_gemm_scatter_kernel<AK, BK_, InT, F32>;
   static bool configured = false;
   if (!configured) {
     C10_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kFusedSmemBytes));
     configured = true;
   }
-  kern<<<p.num_gemm_ctas + p.num_comm_ctas, kGemmThreads, kFusedSmemBytes, stream>>>(ta, tb, p);
+  kern<<<p.num_gemm_ctas + p.num_comm_ctas, kFusedThreads, kFusedSmemBytes, stream>>>(ta, tb, tao, tbo, p);
   C10_CUDA_KERNEL_LAUNCH_CHECK();
 }
 
 template <typename InT, bool F32>
-static void dispatch_ggs(bool ak, bool bk, const CUtensorMap& ta, const CUtensorMap& tb, const GgsParams& p,
-                         cudaStream_t stream) {
-  if (ak && bk) launch_ggs<true, true, InT, F32>(ta, tb, p, stream);
-  else if (ak && !bk) launch_ggs<true, false, InT, F32>(ta, tb, p, stream);
-  else if (!ak && bk) launch_ggs<false, true, InT, F32>(ta, tb, p, stream);
-  else launch_ggs<false, false, InT, F32>(ta, tb, p, stream);
+static void dispatch_ggs(bool ak, bool bk, const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tao,
+                         const CUtensorMap& tbo, const GgsParams& p, cudaStream_t stream) {
+  if (ak && bk) launch_ggs<true, true, InT, F32>(ta, tb, tao, tbo, p, stream);
+  else if (ak && !bk) launch_ggs<true, false, InT, F32>(ta, tb, tao, tbo, p, stream);
+  else if (!ak && bk) launch_ggs<false, true, InT, F32>(ta, tb, tao, tbo, p, stream);
+  else launch_ggs<false, false, InT, F32>(ta, tb, tao, tbo, p, stream);
 }
 
 // One operand's gather, as the host describes it: cfg = [] (not gathered) or [n, me, g, panel_rows, epoch];
@@ -615,10 +701,12 @@ static void fill_gather(const torch::Tensor& t, const std::vector<int64_t>& cfg,
   v.panel_rows = static_cast<int>(cfg[3]);
   v.panels = (v.R + v.panel_rows - 1) / v.panel_rows;
   v.epoch = static_cast<int>(cfg[4]);
+  v.me = me;
+  v.own_direct = 0;
   v.flags = reinterpret_cast<const int*>(flags[me]);
   TORCH_CHECK(v.C % 8 == 0 && n * v.panels <= kKnownWords * 32, "gathered operand: bad shard shape or too many panels");
   TORCH_CHECK(v.g == 0 || v.C % 64 == 0, "column-wise gather needs shard columns in multiples of 64");
-  q.live = 1; q.n = n; q.me = me; q.panels = v.panels; q.epoch = v.epoch;
+  q.live = 1; q.n = n; q.me = me; q.panels = v.panels; q.epoch = v.epoch; q.dests = n;
   q.shard_bytes = static_cast<long long>(v.R) * v.C * 2;
   q.panel_bytes = static_cast<long long>(v.panel_rows) * v.C * 2;
   q.src = reinterpret_cast<const uint8_t*>(t.data_ptr());
@@ -683,6 +771,21 @@ static void gather_gemm_scatter(torch::Tensor a, torch::Tensor b, bool trans_a, 
     if (p.sc_dim == 1 && p.vb.live && p.vb.g == 1 && bk == false) TORCH_CHECK(p.Ns % 64 == 0);
   }
   TORCH_CHECK(out.size(0) == p.Ms && out.size(1) == p.Ns, "output must have the shape of this rank's part");
+  // The own shard is read in place (and not copied into the own gather buffer) whenever no TMA box can cover rows
+  // of two sources: always for a column-wise concatenation; for a row-wise one when the shard extent and every
+  // box origin are multiples of the box height.
+  if (p.va.live) {
+    const int h = ak ? kBM : kBK;
+    const bool origins = !ak || p.sc_dim != 0 || p.Ms % kBM == 0;
+    p.va.own_direct = (p.va.g == 1 || (p.va.R % h == 0 && origins)) ? 1 : 0;
+    if (p.va.own_direct) p.pa.dests = p.pa.n - 1;
+  }
+  if (p.vb.live) {
+    const int h = bk ? kFusedBN : kBK;
+    const bool origins = !bk || p.sc_dim != 1 || p.Ns % kFusedBN == 0;
+    p.vb.own_direct = (p.vb.g == 1 || (p.vb.R % h == 0 && origins)) ? 1 : 0;
+    if (p.vb.own_direct) p.pb.dests = p.pb.n - 1;
+  }
   p.tiles_m = (p.Ms + kBM - 1) / kBM;
   p.tiles_n = (p.Ns + kFusedBN - 1) / kFusedBN;
   p.out = out.data_ptr();
@@ -714,13 +817,15 @@ static void gather_gemm_scatter(torch::Tensor a, torch::Tensor b, bool trans_a, 
   const uint64_t br = p.vb.live ? static_cast<uint64_t>(p.vb.n) * b.size(0) : b.size(0);
   CUtensorMap ta = make_tma_2d(a_ptr, ar, a.size(1), a.size(1), ak ? kBM : 64);
   CUtensorMap tb = make_tma_2d(b_ptr, br, b.size(1), b.size(1), bk ? kFusedBN : 64);
+  CUtensorMap tao = make_tma_2d(a.data_ptr(), a.size(0), a.size(1), a.size(1), ak ? kBM : 64);
+  CUtensorMap tbo = make_tma_2d(b.data_ptr(), b.size(0), b.size(1), b.size(1), bk ? kFusedBN : 64);
   auto stream = at::cuda::getCurrentCUDAStream();
   if (p.is_bf16) {
-    if (f32) dispatch_ggs<__nv_bfloat16, true>(ak, bk, ta, tb, p, stream);
-    else dispatch_ggs<__nv_bfloat16, false>(ak, bk, ta, tb, p, stream);
+    if (f32) dispatch_ggs<__nv_bfloat16, true>(ak, bk, ta, tb, tao, tbo, p, stream);
+    else dispatch_ggs<__nv_bfloat16, false>(ak, bk, ta, tb, tao, tbo, p, stream);
   } else {
-    if (f32) dispatch_ggs<__half, true>(ak, bk, ta, tb, p, stream);
-    else dispatch_ggs<__half, false>(ak, bk, ta, tb, p, stream);
+    if (f32) dispatch_ggs<__half, true>(ak, bk, ta, tb, tao, tbo, p, stream);
+    else dispatch_ggs<__half, false>(ak, bk, ta, tb, tao, tbo, p, stream);
   }
 }
 

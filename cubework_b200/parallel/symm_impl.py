@@ -253,8 +253,10 @@ def fused_gather_gemm_scatter(a, b, trans_a, trans_b, gather_a, gather_b, scatte
             return t
         n, g = plan[0], plan[1]
         R, C = t.shape
-        stacked = m.as_tensor(bufs[cfg[1]], [n, R, C], t.dtype, t.device.index)
-        return stacked.reshape(n * R, C).clone() if g == 0 else stacked.permute(1, 0, 2).reshape(R, n * C)
+        # the buffer holds the other ranks' shards (the own one only in some layouts): copy out, then place the own
+        full = m.as_tensor(bufs[cfg[1]], [n, R, C], t.dtype, t.device.index).clone()
+        full[cfg[1]] = t
+        return full.reshape(n * R, C) if g == 0 else full.permute(1, 0, 2).reshape(R, n * C)
 
     return out, gathered(ga, ga_cfg, ga_bufs, a), gathered(gb, gb_cfg, gb_bufs, b)
 
