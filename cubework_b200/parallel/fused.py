@@ -81,3 +81,18 @@ def gemm_all_reduce_async(a, b, trans_a, trans_b, mode, out_dtype=None):
     if mode.world_size > 1:
         return all_reduce(c, mode, async_op=True)
     return c, None
+
+
+def gemm_reduce_scatter_async(a, b, trans_a, trans_b, scatter: Spec, out_dtype=None):
+    """``(C, work)`` with ``C = reduce-scatter(op(a) @ op(b))``.  The fused kernel does both at once (``work`` is
+    None); otherwise the product is followed by an asynchronous reduce-scatter and ``work.wait()`` must be called
+    before ``C`` is read, so the caller can overlap it with its next product."""
+    out_dtype = out_dtype or a.dtype
+    if not _live(scatter):
+        return ops.gemm(a, b, trans_a, trans_b, out_dtype=out_dtype), None
+    if ops.use_kernels(a) and symm.available():
+        res = symm.fused_gather_gemm_reduce(a, b, trans_a, trans_b, None, None, scatter, None, None, out_dtype, False)
+        if res is not None:
+            return res, None
+    c = ops.gemm(a, b, trans_a, trans_b, out_dtype=out_dtype)
+    return reduce_scatter(c, scatter[1], scatter[0], async_op=True)

@@ -25,7 +25,7 @@ import torch
 from .. import ops
 from ..global_vars import env
 from .collective import all_gather, all_reduce, reduce_scatter
-from .fused import gather_gemm_reduce
+from .fused import gather_gemm_reduce, gemm_reduce_scatter_async
 from .functional import as_compute
 from .mesh import ParallelMode, pm
 from .ops_2d import _GatherParam, _ReduceByBatch, _ReduceScatterTensor, _ReduceTensor, layer_norm_sharded
@@ -117,11 +117,9 @@ class _Linear3D(torch.autograd.Function):
         works = []
         if ctx.needs_input_grad[1]:
             if w_is_out_in:   # dW = dY^T X  [out/d, in/d] -> scatter rows over the weight group
-                dw_full = ops.gemm(dy_full, x_full, trans_a=True, out_dtype=w_dtype)
-                dw, wk = reduce_scatter(dw_full, 0, wm, async_op=True)
+                dw, wk = gemm_reduce_scatter_async(dy_full, x_full, True, False, (wm, 0), out_dtype=w_dtype)
             else:             # dW = X^T dY  [in/d, out/d] -> scatter columns over the weight group
-                dw_full = ops.gemm(x_full, dy_full, trans_a=True, out_dtype=w_dtype)
-                dw, wk = reduce_scatter(dw_full, 1, wm, async_op=True)
+                dw, wk = gemm_reduce_scatter_async(x_full, dy_full, True, False, (wm, 1), out_dtype=w_dtype)
             works.append(wk)
         if b_dtype is not None and ctx.needs_input_grad[2]:
             db, wk = all_reduce(ops.column_sum(dy_full).to(b_dtype), wm, async_op=True)

@@ -40,9 +40,15 @@ def _worker(rank, world_size, port, fn, tp, tp_size, backend, fn_args, use_cuda)
 
 def run_dist(fn, world_size, tp=None, tp_size=None, backend="gloo", args=(), use_cuda=False):
     from cubework_b200.utils import free_port
-    port = free_port()
-    mp.spawn(_worker, args=(world_size, port, fn, tp, tp_size or world_size, backend, args, use_cuda),
-             nprocs=world_size, join=True)
+    for attempt in range(4):
+        port = free_port()
+        try:
+            mp.spawn(_worker, args=(world_size, port, fn, tp, tp_size or world_size, backend, args, use_cuda),
+                     nprocs=world_size, join=True)
+            return
+        except Exception as e:     # the probed port can be taken again before rank 0 binds it: pick another
+            if "address already in use" not in str(e).lower() or attempt == 3:
+                raise
 
 
 def chunk(x, n, dim, idx):

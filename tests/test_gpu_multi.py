@@ -177,9 +177,14 @@ def _check_gpt2_step():
     assert abs(losses[0] - 7.62) < 0.2 and losses[2] < losses[0], losses
 
 
-def _check_model_against_cpu_oracle(family):
-    """bf16 kernel path of a tiny model under the active tensor-parallel mode vs the unsharded fp32 model on the host."""
+def _check_model_against_cpu_oracle(family, force_fused=False):
+    """bf16 kernel path of a tiny model under the active tensor-parallel mode vs the unsharded fp32 model on the host.
+    With ``force_fused`` every product whose layout the fused gather/GEMM/scatter kernels cover goes through them
+    (by default products this small are composed from collectives + GEMM)."""
     from cubework_b200.engine import Trainer
+    from cubework_b200.parallel import symm, symm_impl
+    if force_fused:
+        symm._POLICY = "1"
     from cubework_b200.global_vars import env
     from cubework_b200.ops import ext
     from cubework_b200.optim import FusedAdamW
@@ -205,6 +210,8 @@ def _check_model_against_cpu_oracle(family):
     for a, b in zip(losses, ref_losses):
         assert abs(a - b) < 0.03 * max(1.0, abs(b)), (family, losses, ref_losses)
     assert losses[2] < losses[0]
+    if force_fused:
+        assert symm_impl.STATS["gather_gemm_scatter"] + symm_impl.STATS["gemm_all_reduce"] > 0
 
 
 def _multi(fn, n=2, tp="1d", args=()):
@@ -214,13 +221,13 @@ def _multi(fn, n=2, tp="1d", args=()):
 
 
 def test_2d_models_bf16_four_ranks():
-    for family in ("gpt2", "vit"):
-        _multi(_check_model_against_cpu_oracle, 4, tp="2d", args=(family, ))
+    for family, force in (("gpt2", True), ("vit", False), ("opt", True)):
+        _multi(_check_model_against_cpu_oracle, 4, tp="2d", args=(family, force))
 
 
 def test_3d_models_bf16_eight_ranks():
-    for family in ("gpt2", "vit"):
-        _multi(_check_model_against_cpu_oracle, 8, tp="3d", args=(family, ))
+    for family, force in (("gpt2", True), ("vit", False), ("opt", True)):
+        _multi(_check_model_against_cpu_oracle, 8, tp="3d", args=(family, force))
 
 
 def test_1d_models_bf16_two_ranks():
