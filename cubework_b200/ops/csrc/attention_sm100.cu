@@ -90,7 +90,16 @@ struct AttnParams {
   const float* delta;   // [B, H, T]  rowsum(dO * O)
   float* dq_acc;        // [B, H, T, DP] fp32 scratch, zero-initialised (DP = padded head dim)
   void* dqkv;           // [B, T, H, 3*dh]
+  long long* trace;     // optional [2][4096][2]: (event, globaltimer) stamps of CTA 0 (row 0: softmax group 0, row 1: MMA issuer)
 };
+__device__ __forceinline__ void attn_trace(long long* trace, int row, int& n, int code) {
+  if (trace != nullptr && blockIdx.x == 0 && n < 4096) {
+    long long* e = trace + (static_cast<size_t>(row) * 4096 + n) * 2;
+    e[0] = code;
+    e[1] = static_cast<long long>(globaltimer_ns());
+    ++n;
+  }
+}
 
 // One [128 x 64*NB] tile = NB boxes of 64 columns; arrives on `bar` (expect_tx must cover NB * 16 KB).
 template <int NB>
@@ -305,6 +314,418 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
   }
 }
 
+// ---------------------------------------------------------------------------------------------------------
+// Warp-specialised forward for head dims up to 64: persistent CTAs (one per SM) of ten warps.
+//   warps 0-3 / 4-7  two softmax groups; group w owns the key blocks j = w, w+2, ... of the current query tile,
+//                    with its own running max / sum and its own output accumulator, merged at the end of the tile
+//   warp 8           issues every tcgen05.mma: S_w = Q K_j^T into group w's score columns, O_w += P_w V_j
+//   warp 9           TMA producer: Q (two buffers), K and V (rings of three), key bias (ring of six)
+// While one group runs its exponentials the tensor core works for the other, and the next score block of a group
+// is issued as soon as its P has been handed over, so no group waits for a tensor-core round trip with nothing
+// else resident on the SM.  O accumulates in TMEM across key blocks; the owning group rescales it in place
+// (tcgen05.ld / st) before handing over the next P.  All hand-overs are mbarriers with bounded waits.
+// TMEM: S_0 [0,128)  S_1 [128,256)  O_0 [256,256+DP)  O_1 [320,320+DP).
+// ---------------------------------------------------------------------------------------------------------
+// Warp-specialised forward for head dims up to 64: persistent CTAs (one per SM) of twelve warps that run TWO
+// independent query tiles at a time ("lanes" w = 0, 1), each with its own
+//   softmax group   warps 4w .. 4w+3: thread r owns query row r; two passes over the scores in TMEM (maximum, then
+//                   exponentials), P to shared memory, O rescaled in TMEM, the tile's output written at the end
+//   MMA issuer      warp 8 + w:  S = Q K_j^T, then after the group hands over P_j: O += P_j V_j and S for block j+1
+//   TMA producer    warp 10 + w: Q, K (ring of two), V, key bias (ring of four)
+// While one lane waits for a tensor-core round trip or writes its output, the other lane's group computes, and the
+// MMA / TMA threads never sit on a softmax warp's critical path.  O accumulates in TMEM across key blocks; the group
+// rescales it in place (tcgen05.ld / st) before handing over the next P.  All hand-overs are mbarriers with bounded
+// waits.  TMEM: S_w at 128 w, O_w at 256 + 64 w.
+template <bool MASKED, bool BIAS>
+__device__ __forceinline__ float chunk_max(const uint32_t (&raw)[32], const float* bias, float sc2, int key0, int q_idx, int T,
+                                           bool causal, float m) {
+  float mm[4] = {m, -INFINITY, -INFINITY, -INFINITY};      // four chains: the maximum is not one long dependency
+#pragma unroll
+  for (int i = 0; i < 32; ++i) {
+    float sx = BIAS ? fmaf(__uint_as_float(raw[i]), sc2, bias[i]) : __uint_as_float(raw[i]);
+    if (MASKED) {
+      const int key = key0 + i;
+      if (key >= T || (causal && key > q_idx)) sx = -INFINITY;
+    }
+    mm[i & 3] = fmaxf(mm[i & 3], sx);
+  }
+  return fmaxf(fmaxf(mm[0], mm[1]), fmaxf(mm[2], mm[3]));
+}
+// exponentials of one chunk relative to m_use (log2 domain); returns their sum
+template <bool MASKED, bool BIAS>
+__device__ __forceinline__ float chunk_exp(const uint32_t (&raw)[32], const float* bias, float sc2, float m_use, int key0,
+                                           int q_idx, int T, bool causal, float (&pv)[32]) {
+  float ll[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+  for (int i = 0; i < 32; ++i) {
+    float e = ex2_approx(fmaf(__uint_as_float(raw[i]), sc2, BIAS ? bias[i] - m_use : -m_use));
+    if (MASKED) {
+      const int key = key0 + i;
+      if (key >= T || (causal && key > q_idx)) e = 0.f;
+    }
+    pv[i] = e;
+    ll[i & 3] += e;
+  }
+  return (ll[0] + ll[1]) + (ll[2] + ll[3]);
+}
+
+constexpr int kWsThreads = 384;
+constexpr int kWsKRing = 2, kWsBiasRing = 4;
+template <int DP>
+constexpr int fwd_ws_smem() {
+  return 2 * ((1 + kWsKRing + 1) * kBlk * 128 + 2 * kBlk * 128 + kWsBiasRing * kBlk * 4) + 512 + 1024;
+}
+
+struct WsLaneBars {
+  uint64_t q_full, q_empty;
+  uint64_t k_full[kWsKRing], k_empty[kWsKRing];
+  uint64_t v_full, v_empty;
+  uint64_t s_full, p_ready, o_full;
+};
+
+template <typename T, int DP>
+__global__ void __launch_bounds__(kWsThreads, 1)
+attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+                   const __grid_constant__ CUtensorMap map_v, AttnParams p) {
+  static_assert(DP <= 64, "one 64-column image per operand");
+  constexpr int kImg = kBlk * 128;                 // 16 KB: a [128 x 64] 16-bit image
+  constexpr int kPImg = 2 * kBlk * 128;            // 32 KB: a [128 x 128] 16-bit image
+  constexpr int kLaneBytes = (1 + kWsKRing + 1) * kImg + kPImg + kWsBiasRing * kBlk * 4;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  WsLaneBars* all_bars = reinterpret_cast<WsLaneBars*>(smem + 2 * kLaneBytes);
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(all_bars + 2);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (threadIdx.x == 0) {
+    for (int w = 0; w < 2; ++w) {
+      WsLaneBars* bb = all_bars + w;
+      mbar_init(&bb->q_full, 1); mbar_init(&bb->q_empty, 1);
+      for (int i = 0; i < kWsKRing; ++i) { mbar_init(&bb->k_full[i], 1); mbar_init(&bb->k_empty[i], 1); }
+      mbar_init(&bb->v_full, 1); mbar_init(&bb->v_empty, 1);
+      mbar_init(&bb->s_full, 1); mbar_init(&bb->p_ready, kBlk); mbar_init(&bb->o_full, 1);
+    }
+    *abort_flag = 0;
+    fence_barrier_init();
+  }
+  if (warp == 8) {
+    __syncwarp();
+    tmem_alloc(tmem_slot, 512);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = *tmem_slot;
+
+  // this thread's lane and that lane's buffers
+  const int w = warp < 8 ? warp >> 2 : (warp - 8) & 1;
+  uint8_t* lane_smem = smem + w * kLaneBytes;
+  uint8_t* q_img = lane_smem;
+  uint8_t* k_img = q_img + kImg;                   // [kWsKRing]
+  uint8_t* v_img = k_img + kWsKRing * kImg;
+  uint8_t* p_img = v_img + kImg;
+  float* s_bias = reinterpret_cast<float*>(p_img + kPImg);          // [kWsBiasRing][128], log2 domain
+  WsLaneBars* bars = all_bars + w;
+  const uint32_t tm_s = tmem + w * 128, tm_o = tmem + 256 + w * 64;
+
+  const int n_qb = (p.T + kBlk - 1) / kBlk;
+  const int bh_total = p.B * p.H;
+  const int tiles = n_qb * bh_total;
+  const bool has_bias = p.key_bias != nullptr;
+  auto n_kv_of = [&](int qb) { return p.causal ? min(n_qb, qb + 1) : n_qb; };
+  // tiles of this lane, heaviest (most key blocks) first: t = first, first + stride, ...
+  const int first = blockIdx.x + w * gridDim.x, stride = 2 * gridDim.x;
+
+  if (warp >= 10) {
+    // =========================================================================== TMA producer (+ key bias)
+    int kcount = 0, vcount = 0, tile_it = 0;
+    for (int t = first; t < tiles; t += stride, ++tile_it) {
+      if (__shfl_sync(0xffffffffu, lane == 0 ? *abort_flag : 0, 0)) break;     // one decision for the whole warp
+      const int qb = n_qb - 1 - t / bh_total, bh = t % bh_total;
+      const int h = bh % p.H, b = bh / p.H;
+      const int n_kv = n_kv_of(qb);
+      bool ok = true;
+      if (lane == 0) {
+        ok = mbar_wait(&bars->q_empty, (tile_it & 1) ^ 1, abort_flag, p.status, kErrAttnBarrierTimeout, t);
+        if (ok) {
+          mbar_expect_tx(&bars->q_full, kImg);
+          tma_load_4d(q_img, &map_q, &bars->q_full, 0, qb * kBlk, h, b);
+        }
+      }
+      for (int j = 0; j < n_kv; ++j) {
+        const int ks = kcount % kWsKRing;
+        if (lane == 0)
+          ok = ok && mbar_wait(&bars->k_empty[ks], ((kcount / kWsKRing) & 1) ^ 1, abort_flag, p.status, kErrAttnBarrierTimeout, t);
+        ok = __shfl_sync(0xffffffffu, ok, 0);
+        if (!ok) break;
+        if (has_bias) {
+          float* dst = s_bias + (kcount % kWsBiasRing) * kBlk;
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            const int key = j * kBlk + lane * 4 + i;
+            dst[lane * 4 + i] = key < p.T ? p.key_bias[static_cast<int64_t>(b) * p.T + key] * kLog2e : 0.f;
+          }
+          __threadfence_block();
+        }
+        __syncwarp();
+        if (lane == 0) {
+          mbar_expect_tx(&bars->k_full[ks], kImg);
+          tma_load_4d(k_img + ks * kImg, &map_k, &bars->k_full[ks], 0, j * kBlk, h, b);
+          ok = mbar_wait(&bars->v_empty, (vcount & 1) ^ 1, abort_flag, p.status, kErrAttnBarrierTimeout, t);
+          if (ok) {
+            mbar_expect_tx(&bars->v_full, kImg);
+            tma_load_4d(v_img, &map_v, &bars->v_full, 0, j * kBlk, h, b);
+          }
+        }
+        ++kcount; ++vcount;
+      }
+      ok = __shfl_sync(0xffffffffu, ok, 0);
+      if (!ok) break;
+    }
+  } else if (warp >= 8) {
+    // =========================================================================== MMA issuer of lane w
+    if (lane == 0) {
+      const uint32_t idesc_s = make_idesc_f16(kBlk, kBlk, false, false, p.is_bf16);
+      const uint32_t idesc_o = make_idesc_f16(kBlk, DP, false, true, p.is_bf16);
+      int kcount = 0, vcount = 0, pcount = 0, tile_it = 0;
+      bool ok = true;
+      auto issue_s = [&](bool last) -> bool {
+        const int ks = kcount % kWsKRing;
+        if (!mbar_wait(&bars->k_full[ks], (kcount / kWsKRing) & 1, abort_flag, p.status, kErrAttnBarrierTimeout, kcount)) return false;
+        tc_fence_after();
+#pragma unroll
+        for (int k16 = 0; k16 < DP / 16; ++k16)
+          tc_mma_f16(tm_s, kmajor_desc(smem_u32(q_img), k16), kmajor_desc(smem_u32(k_img + ks * kImg), k16), idesc_s, k16 > 0);
+        tc_commit(&bars->k_empty[ks]);
+        tc_commit(&bars->s_full);
+        if (last) tc_commit(&bars->q_empty);
+        ++kcount;
+        return true;
+      };
+      for (int t = first; t < tiles && ok && !*abort_flag; t += stride, ++tile_it) {
+        const int qb = n_qb - 1 - t / bh_total;
+        const int n_kv = n_kv_of(qb);
+        ok = mbar_wait(&bars->q_full, tile_it & 1, abort_flag, p.status, kErrAttnBarrierTimeout, t);
+        ok = ok && issue_s(n_kv == 1);
+        for (int j = 0; j < n_kv && ok; ++j) {
+          ok = mbar_wait(&bars->p_ready, pcount & 1, abort_flag, p.status, kErrAttnBarrierTimeout, t);
+          if (!ok) break;
+          ++pcount;
+          ok = mbar_wait(&bars->v_full, vcount & 1, abort_flag, p.status, kErrAttnBarrierTimeout, t);
+          if (!ok) break;
+          tc_fence_after();
+#pragma unroll
+          for (int k16 = 0; k16 < kBlk / 16; ++k16)
+            tc_mma_f16(tm_o, kmajor_desc(smem_u32(p_img), k16), mnmajor_desc(smem_u32(v_img), k16), idesc_o,
+                       (j > 0 || k16 > 0) ? 1u : 0u);
+          tc_commit(&bars->v_empty);
+          tc_commit(&bars->o_full);
+          ++vcount;
+          if (j + 1 < n_kv) ok = issue_s(j + 1 == n_kv - 1);
+        }
+      }
+    }
+  } else {
+    // =========================================================================== softmax group of lane w
+    const int r = threadIdx.x & 127;                 // query row inside the tile == TMEM lane
+    const int wq = warp & 3;                         // this warp's 32-row block
+    const uint32_t lane_base = static_cast<uint32_t>(wq * 32) << 16;
+    const float sc2 = p.scale * kLog2e;
+    int scount = 0, ocount = 0, kbase = 0;           // uses of s_full / o_full; key blocks before this tile
+    bool ok = true;
+    int ntr = 0;
+    long long* tr = threadIdx.x == 0 ? p.trace : nullptr;
+    for (int t = first; t < tiles && ok; t += stride) {
+      const int qb = n_qb - 1 - t / bh_total, bh = t % bh_total;
+      const int h = bh % p.H, b = bh / p.H;
+      const int n_kv = n_kv_of(qb);
+      const int q_idx = qb * kBlk + r;
+      float m_run = -INFINITY, l_run = 0.f;
+      for (int j = 0; j < n_kv; ++j) {
+        const int k0 = j * kBlk;
+        attn_trace(tr, 0, ntr, 1);
+        if (!mbar_wait(&bars->s_full, scount & 1, abort_flag, p.status, kErrAttnBarrierTimeout, t)) { ok = false; break; }
+        ++scount;
+        tc_fence_after();
+        attn_trace(tr, 0, ntr, 2);
+        const bool tail = k0 + kBlk > p.T;
+        const bool cdiag = p.causal && j == qb;
+        const float* bias_j = s_bias + ((kbase + j) % kWsBiasRing) * kBlk;
+        const uint32_t s_addr = tm_s + lane_base;
+        uint32_t ra[32], rb[32];
+        float m_blk = -INFINITY;
+        // ---- pass 1: the row maximum.  The next chunk's TMEM load is in flight while the current one is reduced.
+        if (!tail && !cdiag) {
+          // all four chunk loads are issued before the first is used: one TMEM round trip for the pass
+          uint32_t rc[32], rd[32];
+          tmem_ld_32x32(s_addr, ra);
+          tmem_ld_32x32(s_addr + 32, rb);
+          tmem_ld_32x32(s_addr + 64, rc);
+          tmem_ld_32x32(s_addr + 96, rd);
+          tmem_wait_ld_for(ra);
+          tmem_wait_ld_for(rb);
+          tmem_wait_ld_for(rc);
+          tmem_wait_ld_for(rd);
+#define CW_MAX_STEP(CUR, C)                                                                                   \
+          m_blk = has_bias ? chunk_max<false, true>(CUR, bias_j + (C) * 32, sc2, 0, 0, 0, false, m_blk)        \
+                           : chunk_max<false, false>(CUR, nullptr, sc2, 0, 0, 0, false, m_blk);
+          CW_MAX_STEP(ra, 0)
+          CW_MAX_STEP(rb, 1)
+          CW_MAX_STEP(rc, 2)
+          CW_MAX_STEP(rd, 3)
+#undef CW_MAX_STEP
+        } else {
+          // diagonal block of a causal mask: chunks left of this warp's rows are plain, the chunk on the diagonal is
+          // tested key by key, chunks to the right contribute nothing.  A sequence tail is tested everywhere.
+#pragma unroll 1
+          for (int c = 0; c < 4; ++c) {
+            if (!tail && c > wq) break;
+            tmem_ld_32x32(s_addr + c * 32, ra);
+            tmem_wait_ld_for(ra);
+            if (!tail && c < wq)
+              m_blk = has_bias ? chunk_max<false, true>(ra, bias_j + c * 32, sc2, 0, 0, 0, false, m_blk)
+                               : chunk_max<false, false>(ra, nullptr, sc2, 0, 0, 0, false, m_blk);
+            else
+              m_blk = has_bias ? chunk_max<true, true>(ra, bias_j + c * 32, sc2, k0 + c * 32, q_idx, p.T, cdiag, m_blk)
+                               : chunk_max<true, false>(ra, nullptr, sc2, k0 + c * 32, q_idx, p.T, cdiag, m_blk);
+          }
+        }
+        if (!has_bias) m_blk *= sc2;                  // scale > 0: the maximum commutes with the scaling
+        attn_trace(tr, 0, ntr, 3);
+        const float m_new = fmaxf(m_run, m_blk);
+        const float m_use = (m_new == -INFINITY) ? 0.f : m_new;
+        const float alpha = (m_run == -INFINITY) ? 0.f : ex2_approx(m_run - m_use);
+        m_run = m_new;
+        if (j > 0) {
+          // the previous P V has landed in O: rescale it in place before more is added
+          if (!mbar_wait(&bars->o_full, ocount & 1, abort_flag, p.status, kErrAttnBarrierTimeout, t)) { ok = false; break; }
+          ++ocount;
+          tc_fence_after();
+          attn_trace(tr, 0, ntr, 4);
+          if (__any_sync(0xffffffffu, alpha != 1.f)) {
+#pragma unroll
+            for (int c = 0; c < DP / 32; ++c) {
+              uint32_t raw[32];
+              tmem_ld_32x32(tm_o + lane_base + c * 32, raw);
+              tmem_wait_ld_for(raw);
+#pragma unroll
+              for (int i = 0; i < 32; ++i) raw[i] = __float_as_uint(__uint_as_float(raw[i]) * alpha);
+              tmem_st_32x32(tm_o + lane_base + c * 32, raw);
+            }
+            tmem_wait_st();
+          }
+        }
+        // ---- pass 2: exponentials, P to shared memory
+        float l_blk = 0.f;
+        attn_trace(tr, 0, ntr, 5);
+        if (!tail && !cdiag) {
+          // chunks 0 and 1 are requested together; chunk c + 2 is requested before chunk c is processed
+          uint32_t rc[32];
+          tmem_ld_32x32(s_addr, ra);
+          tmem_ld_32x32(s_addr + 32, rb);
+          tmem_wait_ld_for(ra);
+          tmem_wait_ld_for(rb);
+#define CW_EXP_STEP(CUR, C)                                                                                   \
+          {                                                                                                    \
+            float pv[32];                                                                                      \
+            l_blk += has_bias ? chunk_exp<false, true>(CUR, bias_j + (C) * 32, sc2, m_use, 0, 0, 0, false, pv) \
+                              : chunk_exp<false, false>(CUR, nullptr, sc2, m_use, 0, 0, 0, false, pv);         \
+            store_p_chunk<T>(p_img, r, (C) * 32, pv);                                                          \
+          }
+          tmem_ld_32x32(s_addr + 64, rc);
+          CW_EXP_STEP(ra, 0)
+          tmem_wait_ld_for(rc);
+          tmem_ld_32x32(s_addr + 96, ra);
+          CW_EXP_STEP(rb, 1)
+          tmem_wait_ld_for(ra);
+          CW_EXP_STEP(rc, 2)
+          CW_EXP_STEP(ra, 3)
+#undef CW_EXP_STEP
+        } else {
+#pragma unroll 1
+          for (int c = 0; c < 4; ++c) {
+            float pv[32];
+            if (!tail && c > wq) {
+#pragma unroll
+              for (int i = 0; i < 32; ++i) pv[i] = 0.f;
+            } else {
+              tmem_ld_32x32(s_addr + c * 32, ra);
+              tmem_wait_ld_for(ra);
+              if (!tail && c < wq)
+                l_blk += has_bias ? chunk_exp<false, true>(ra, bias_j + c * 32, sc2, m_use, 0, 0, 0, false, pv)
+                                  : chunk_exp<false, false>(ra, nullptr, sc2, m_use, 0, 0, 0, false, pv);
+              else
+                l_blk += has_bias ? chunk_exp<true, true>(ra, bias_j + c * 32, sc2, m_use, k0 + c * 32, q_idx, p.T, cdiag, pv)
+                                  : chunk_exp<true, false>(ra, nullptr, sc2, m_use, k0 + c * 32, q_idx, p.T, cdiag, pv);
+            }
+            store_p_chunk<T>(p_img, r, c * 32, pv);
+          }
+        }
+        l_run = l_run * alpha + l_blk;
+        attn_trace(tr, 0, ntr, 6);
+        fence_proxy_async();
+        tc_fence_before();
+        mbar_arrive(&bars->p_ready);
+        attn_trace(tr, 0, ntr, 7);
+      }
+      if (!ok) break;
+      // ---- the tile's output: the last P V has landed
+      if (!mbar_wait(&bars->o_full, ocount & 1, abort_flag, p.status, kErrAttnBarrierTimeout, t)) { ok = false; break; }
+      ++ocount;
+      tc_fence_after();
+      attn_trace(tr, 0, ntr, 8);
+      {
+        // rows go through shared memory (the P image is free now) so that each global store instruction writes one
+        // row's contiguous bytes instead of one column of 32 rows that lie kilobytes apart
+        const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
+        T* stage = reinterpret_cast<T*>(p_img) + wq * 32 * DP;          // this warp's [32][DP]
+#pragma unroll
+        for (int c = 0; c < DP / 32; ++c) {
+          uint32_t raw[32];
+          tmem_ld_32x32(tm_o + lane_base + c * 32, raw);
+          tmem_wait_ld_for(raw);
+          uint4* dst = reinterpret_cast<uint4*>(stage + lane * DP + c * 32);
+#pragma unroll
+          for (int q = 0; q < 4; ++q) {
+            uint4 u;
+            u.x = pack_pair<T>(__uint_as_float(raw[q * 8 + 0]) * inv, __uint_as_float(raw[q * 8 + 1]) * inv);
+            u.y = pack_pair<T>(__uint_as_float(raw[q * 8 + 2]) * inv, __uint_as_float(raw[q * 8 + 3]) * inv);
+            u.z = pack_pair<T>(__uint_as_float(raw[q * 8 + 4]) * inv, __uint_as_float(raw[q * 8 + 5]) * inv);
+            u.w = pack_pair<T>(__uint_as_float(raw[q * 8 + 6]) * inv, __uint_as_float(raw[q * 8 + 7]) * inv);
+            dst[q] = u;
+          }
+        }
+        if (q_idx < p.T)
+          p.lse[(static_cast<int64_t>(b) * p.H + h) * p.T + q_idx] = (l_run > 0.f) ? m_run + log2f(l_run) : -INFINITY;
+        tc_fence_before();
+        __syncwarp();
+        const int row0 = qb * kBlk + wq * 32;
+        T* o = reinterpret_cast<T*>(p.out) + ((static_cast<int64_t>(b) * p.T + row0) * p.H + h) * p.dh;
+        const int64_t row_pitch = static_cast<int64_t>(p.H) * p.dh;
+        const int rows = min(32, p.T - row0);
+        for (int rr = 0; rr < rows; ++rr)
+          for (int d = lane; d < p.dh; d += 32) o[rr * row_pitch + d] = stage[rr * DP + d];
+        __syncwarp();
+      }
+      attn_trace(tr, 0, ntr, 9);
+      kbase += n_kv;
+    }
+    if (!ok) *abort_flag = 1;
+  }
+
+  if (*abort_flag) {
+    for (int i = 0; i < 32; ++i) __nanosleep(1000);
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 8) {
+    tc_fence_after();
+    tmem_dealloc(tmem, 512);
+  }
+}
+
 // Copy `parts` consecutive [dh] slices per (token, head) of src [B, T, H, parts*dh] into zero-padded rows
 // dst [parts][B, H, T, W] (W a multiple of 64): makes every row 16-byte aligned for TMA.
 template <typename T>
@@ -358,13 +779,40 @@ __global__ void attn_dq_store_kernel(const float* __restrict__ dq_acc, T* __rest
   dqkv[bth * 3 * dh + d] = from_f<T>(dq_acc[((static_cast<int64_t>(b) * H + h) * Tn + t) * DP + d]);
 }
 
+// P and dS of one 32-score chunk of a row.  p = exp2(s*sc2 + bias - lse), ds = p * (dp - delta) * scale.
+template <bool MASKED, bool BIAS, typename T>
+__device__ __forceinline__ void bwd_chunk(const uint32_t (&rs)[32], const uint32_t (&rp)[32], const float* bias, float sc2,
+                                          float lse2, float scale, float nds, int key0, int q_idx, int Tn, bool causal,
+                                          uint8_t* p_img, uint8_t* ds_img, int r, int c0) {
+  float pv[32], dsv[32];
+#pragma unroll
+  for (int j = 0; j < 32; ++j) {
+    float pr = ex2_approx(fmaf(__uint_as_float(rs[j]), sc2, BIAS ? bias[j] - lse2 : -lse2));
+    if (MASKED) {
+      const int key = key0 + j;
+      if (key >= Tn || q_idx >= Tn || (causal && key > q_idx)) pr = 0.f;
+    }
+    pv[j] = pr;
+    dsv[j] = pr * fmaf(__uint_as_float(rp[j]), scale, nds);
+  }
+  store_p_chunk<T>(p_img, r, c0, pv);
+  store_p_chunk<T>(ds_img, r, c0, dsv);
+}
+
+constexpr int kBwdThreads = 256;   // two threads per query row: each handles 64 of the 128 keys of a block
+
 template <typename T, int DP>
-__global__ void __launch_bounds__(kAttnThreads)
+__global__ void __launch_bounds__(kBwdThreads, 1)
 attn_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                 const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_do, AttnParams p) {
   constexpr int NB = (DP + 63) / 64;
   constexpr int kImg = NB * kBlk * 128;
-  constexpr uint32_t kTmemCols = 512;   // S/dQ: [0,128)  dP: [128,256)  dV: [256,256+DP)  dK: [384,384+DP)
+  constexpr uint32_t kTmemCols = 512;
+  // TMEM columns.  DP <= 64: S [0,128) dP [128,256) dV [256,..) dK [320,..) dQ [384,..): dQ has columns of its own, so
+  // the scores of the next query block are multiplied while this block's dQ is being written out.
+  // DP > 64: S/dQ [0,128) dP [128,256) dV [256,..) dK [384,..) (dQ reuses the score columns).
+  constexpr bool kSep = DP <= 64;
+  constexpr uint32_t kColDV = 256, kColDK = kSep ? 320 : 384, kColDQ = kSep ? 384 : 0;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* k_img = smem;
@@ -380,16 +828,19 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
   float* s_bias = reinterpret_cast<float*>(tmem_slot + 2);                 // [128] key bias (log2 domain) of this block
   float* dq_stage = reinterpret_cast<float*>(p_img);                       // [128][DP] fp32, aliases P / dS between uses
 
-  const int r = threadIdx.x, warp = r >> 5;
+  const int tid = threadIdx.x, warp = tid >> 5;
+  const int r = tid & 127;                         // query row inside a block == TMEM lane
+  const int half = tid >> 7;                       // which 64 keys of the block this thread handles
   const int kb = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
   const int k0 = kb * kBlk;
   const int64_t ld = static_cast<int64_t>(p.H) * 3 * p.dh;
   const float* kbias = p.key_bias != nullptr ? p.key_bias + static_cast<int64_t>(b) * p.T : nullptr;
-  if (kbias != nullptr) s_bias[r] = k0 + r < p.T ? kbias[k0 + r] * kLog2e : 0.f;
+  const bool has_bias = kbias != nullptr;
+  if (has_bias && tid < kBlk) s_bias[tid] = k0 + tid < p.T ? kbias[k0 + tid] * kLog2e : 0.f;
   const int n_q = (p.T + kBlk - 1) / kBlk;
   const int i0 = p.causal ? kb : 0;
 
-  if (r == 0) {
+  if (tid == 0) {
     for (int i = 0; i < 5; ++i) mbar_init(&bars[i], 1);
     *abort_flag = 0;
     fence_barrier_init();
@@ -401,6 +852,11 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
       tma_tile<NB>(q_img0, &map_q, &bars[3], i0 * kBlk, h, b);
       tma_tile<NB>(do_img0, &map_do, &bars[3], i0 * kBlk, h, b);
     }
+    if (kBufs == 2 && i0 + 1 < n_q) {
+      mbar_expect_tx(&bars[4], 2 * kImg);
+      tma_tile<NB>(q_img0 + kImg, &map_q, &bars[4], (i0 + 1) * kBlk, h, b);
+      tma_tile<NB>(do_img0 + kImg, &map_do, &bars[4], (i0 + 1) * kBlk, h, b);
+    }
   }
   if (warp == 0) {
     __syncwarp();   // lane 0 just left the set-up branch: the allocation is warp-collective
@@ -411,105 +867,139 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = *tmem_slot;
-  const uint32_t lane_base = static_cast<uint32_t>(warp * 32) << 16;
+  const uint32_t lane_base = static_cast<uint32_t>((warp & 3) * 32) << 16;
   const uint32_t idesc_s = make_idesc_f16(kBlk, kBlk, false, false, p.is_bf16);     // Q K^T, dO V^T
   const uint32_t idesc_tt = make_idesc_f16(kBlk, DP, true, true, p.is_bf16);        // P^T dO, dS^T Q
   const uint32_t idesc_dq = make_idesc_f16(kBlk, DP, false, true, p.is_bf16);       // dS K
   const float sc2 = p.scale * kLog2e;
 
+  // S = Q K^T and dP = dO V^T of the query block held in buffer `sb` (thread 0 only)
+  auto issue_scores = [&](int it, int sb) -> bool {
+    const uint32_t parity = kBufs == 2 ? ((it >> 1) & 1) : (it & 1);
+    bool good = true;
+    if (it == 0) good = mbar_wait(&bars[2], 0, abort_flag, p.status, kErrAttnBarrierTimeout, blockIdx.x);
+    good = good && mbar_wait(&bars[3 + sb], parity, abort_flag, p.status, kErrAttnBarrierTimeout, blockIdx.x);
+    if (!good) return false;
+    tc_fence_after();
+    const uint32_t qa = smem_u32(q_img0 + sb * kImg), da = smem_u32(do_img0 + sb * kImg);
+#pragma unroll
+    for (int k16 = 0; k16 < DP / 16; ++k16)
+      tc_mma_f16(tmem, kmajor_desc(qa, k16), kmajor_desc(smem_u32(k_img), k16), idesc_s, k16 > 0);
+#pragma unroll
+    for (int k16 = 0; k16 < DP / 16; ++k16)
+      tc_mma_f16(tmem + 128, kmajor_desc(da, k16), kmajor_desc(smem_u32(v_img), k16), idesc_s, k16 > 0);
+    tc_commit(&bars[0]);
+    return true;
+  };
+
   bool ok = true;
   int it = 0;
+  if (kSep && tid == 0 && i0 < n_q) issue_scores(0, 0);
   for (int i = i0; i < n_q && ok; ++i, ++it) {
     const int q0 = i * kBlk;
     const int sb = kBufs == 2 ? (it & 1) : 0;
-    const uint32_t qdo_parity = kBufs == 2 ? ((it >> 1) & 1) : (it & 1);
     uint8_t* q_img = q_img0 + sb * kImg;
     uint8_t* do_img = do_img0 + sb * kImg;
     const int q_idx = q0 + r;
     const int64_t stat = (static_cast<int64_t>(b) * p.H + h) * p.T + q_idx;
     const float lse2 = q_idx < p.T ? p.lse[stat] : 0.f;
-    const float dlt = q_idx < p.T ? p.delta[stat] : 0.f;
-    // every thread has finished reading dQ (aliased with S) of the previous query block, and the bulk reduction
-    // of that block has finished reading its staging area (aliased with P / dS)
-    if (r == 0) bulk_wait_group_read0();
+    const float nds = q_idx < p.T ? -p.delta[stat] * p.scale : 0.f;
+    // every thread has finished reading dQ of the previous query block, and the bulk reduction of that block has
+    // finished reading its staging area (aliased with P / dS)
+    if (tid == 0) bulk_wait_group_read0();
     tc_fence_before();
     __syncthreads();
-    if (r == 0) {
-      bool good = true;
-      if (it == 0) good = mbar_wait(&bars[2], 0, abort_flag, p.status, kErrAttnBarrierTimeout, blockIdx.x);
-      good = good && mbar_wait(&bars[3 + sb], qdo_parity, abort_flag, p.status, kErrAttnBarrierTimeout, blockIdx.x);
-      if (good) {
-        tc_fence_after();
-#pragma unroll
-        for (int k16 = 0; k16 < DP / 16; ++k16)
-          tc_mma_f16(tmem, kmajor_desc(smem_u32(q_img), k16), kmajor_desc(smem_u32(k_img), k16), idesc_s, k16 > 0);
-#pragma unroll
-        for (int k16 = 0; k16 < DP / 16; ++k16)
-          tc_mma_f16(tmem + 128, kmajor_desc(smem_u32(do_img), k16), kmajor_desc(smem_u32(v_img), k16), idesc_s, k16 > 0);
-        tc_commit(&bars[0]);
-        if (kBufs == 2 && i + 1 < n_q) {          // the other Q / dO buffer was released by the previous bars[1] wait
-          mbar_expect_tx(&bars[3 + (sb ^ 1)], 2 * kImg);
-          tma_tile<NB>(q_img0 + (sb ^ 1) * kImg, &map_q, &bars[3 + (sb ^ 1)], q0 + kBlk, h, b);
-          tma_tile<NB>(do_img0 + (sb ^ 1) * kImg, &map_do, &bars[3 + (sb ^ 1)], q0 + kBlk, h, b);
-        }
-      }
-    }
+    if (!kSep && tid == 0) issue_scores(it, sb);
     if (!mbar_wait(&bars[0], it & 1, abort_flag, p.status, kErrAttnBarrierTimeout, blockIdx.x)) { ok = false; break; }
     tc_fence_after();
-    const bool diag = (p.causal && i == kb) || (k0 + kBlk > p.T) || (q0 + kBlk > p.T);
+    const bool tail = (k0 + kBlk > p.T) || (q0 + kBlk > p.T);
+    const bool cdiag = p.causal && i == kb;
+    const int wq = warp & 3;                       // this warp's 32-row block
+    const int c_a = half * 2, c_b = half * 2 + 1;  // this thread's two 32-key chunks
+    if (!tail && !cdiag) {
+      // the second pair of TMEM loads is in flight while the first is processed
+      uint32_t rs_a[32], rp_a[32], rs_b[32], rp_b[32];
+      tmem_ld_32x32(tmem + lane_base + c_a * 32, rs_a);
+      tmem_ld_32x32(tmem + 128 + lane_base + c_a * 32, rp_a);
+      tmem_wait_ld_for(rs_a);
+      tmem_wait_ld_for(rp_a);
+      tmem_ld_32x32(tmem + lane_base + c_b * 32, rs_b);
+      tmem_ld_32x32(tmem + 128 + lane_base + c_b * 32, rp_b);
+      if (has_bias) bwd_chunk<false, true, T>(rs_a, rp_a, s_bias + c_a * 32, sc2, lse2, p.scale, nds, 0, 0, 0, false, p_img, ds_img, r, c_a * 32);
+      else bwd_chunk<false, false, T>(rs_a, rp_a, nullptr, sc2, lse2, p.scale, nds, 0, 0, 0, false, p_img, ds_img, r, c_a * 32);
+      tmem_wait_ld_for(rs_b);
+      tmem_wait_ld_for(rp_b);
+      if (has_bias) bwd_chunk<false, true, T>(rs_b, rp_b, s_bias + c_b * 32, sc2, lse2, p.scale, nds, 0, 0, 0, false, p_img, ds_img, r, c_b * 32);
+      else bwd_chunk<false, false, T>(rs_b, rp_b, nullptr, sc2, lse2, p.scale, nds, 0, 0, 0, false, p_img, ds_img, r, c_b * 32);
+    } else {
+      // diagonal block of a causal mask: key chunks left of this warp's rows are plain, the chunk on the diagonal is
+      // tested key by key, chunks to the right are zero.  Blocks that reach past the sequence end are tested everywhere.
 #pragma unroll 1
-    for (int c = 0; c < 4; ++c) {
-      uint32_t rs[32], rp[32];
-      tmem_ld_32x32(tmem + lane_base + c * 32, rs);
-      tmem_ld_32x32(tmem + 128 + lane_base + c * 32, rp);
-      tmem_wait_ld();
-      float pv[32], dsv[32];
+      for (int cc = 0; cc < 2; ++cc) {
+        const int c = half * 2 + cc;
+        if (!tail && c > wq) {
+          float z[32];
 #pragma unroll
-      for (int j = 0; j < 32; ++j) {
-        const int key = k0 + c * 32 + j;
-        float sx = __uint_as_float(rs[j]) * sc2;
-        if (kbias != nullptr) sx += s_bias[c * 32 + j];
-        const bool masked = diag && (key >= p.T || q_idx >= p.T || (p.causal && key > q_idx));
-        const float pr = masked ? 0.f : exp2f(sx - lse2);
-        pv[j] = pr;
-        dsv[j] = pr * (__uint_as_float(rp[j]) - dlt) * p.scale;
+          for (int j = 0; j < 32; ++j) z[j] = 0.f;
+          store_p_chunk<T>(p_img, r, c * 32, z);
+          store_p_chunk<T>(ds_img, r, c * 32, z);
+          continue;
+        }
+        uint32_t rs[32], rp[32];
+        tmem_ld_32x32(tmem + lane_base + c * 32, rs);
+        tmem_ld_32x32(tmem + 128 + lane_base + c * 32, rp);
+        tmem_wait_ld_for(rs);
+        tmem_wait_ld_for(rp);
+        if (!tail && c < wq) {
+          if (has_bias) bwd_chunk<false, true, T>(rs, rp, s_bias + c * 32, sc2, lse2, p.scale, nds, 0, 0, 0, false, p_img, ds_img, r, c * 32);
+          else bwd_chunk<false, false, T>(rs, rp, nullptr, sc2, lse2, p.scale, nds, 0, 0, 0, false, p_img, ds_img, r, c * 32);
+        } else {
+          if (has_bias) bwd_chunk<true, true, T>(rs, rp, s_bias + c * 32, sc2, lse2, p.scale, nds, k0 + c * 32, q_idx, p.T, cdiag, p_img, ds_img, r, c * 32);
+          else bwd_chunk<true, false, T>(rs, rp, nullptr, sc2, lse2, p.scale, nds, k0 + c * 32, q_idx, p.T, cdiag, p_img, ds_img, r, c * 32);
+        }
       }
-      store_p_chunk<T>(p_img, r, c * 32, pv);
-      store_p_chunk<T>(ds_img, r, c * 32, dsv);
     }
     fence_proxy_async();
     tc_fence_before();
     __syncthreads();
-    if (r == 0) {
+    if (tid == 0) {
       tc_fence_after();
       const uint32_t acc = it > 0 ? 1u : 0u;
 #pragma unroll
+      for (int k16 = 0; k16 < kBlk / 16; ++k16)   // dQ[q, d] = sum_key dS[q, key] K[key, d]
+        tc_mma_f16(tmem + kColDQ, kmajor_desc(smem_u32(ds_img), k16), mnmajor_desc(smem_u32(k_img), k16), idesc_dq, k16 > 0);
+#pragma unroll
       for (int k16 = 0; k16 < kBlk / 16; ++k16)   // dV[key, d] += sum_q P[q, key] dO[q, d]
-        tc_mma_f16(tmem + 256, mnmajor_desc(smem_u32(p_img), k16), mnmajor_desc(smem_u32(do_img), k16), idesc_tt,
+        tc_mma_f16(tmem + kColDV, mnmajor_desc(smem_u32(p_img), k16), mnmajor_desc(smem_u32(do_img), k16), idesc_tt,
                    (k16 > 0) ? 1u : acc);
 #pragma unroll
       for (int k16 = 0; k16 < kBlk / 16; ++k16)   // dK[key, d] += sum_q dS[q, key] Q[q, d]
-        tc_mma_f16(tmem + 384, mnmajor_desc(smem_u32(ds_img), k16), mnmajor_desc(smem_u32(q_img), k16), idesc_tt,
+        tc_mma_f16(tmem + kColDK, mnmajor_desc(smem_u32(ds_img), k16), mnmajor_desc(smem_u32(q_img), k16), idesc_tt,
                    (k16 > 0) ? 1u : acc);
-#pragma unroll
-      for (int k16 = 0; k16 < kBlk / 16; ++k16)   // dQ[q, d] = sum_key dS[q, key] K[key, d]
-        tc_mma_f16(tmem, kmajor_desc(smem_u32(ds_img), k16), mnmajor_desc(smem_u32(k_img), k16), idesc_dq, k16 > 0);
       tc_commit(&bars[1]);
+      // the scores of the next query block, behind this block's dQ write-out
+      if (kSep && i + 1 < n_q) issue_scores(it + 1, kBufs == 2 ? (sb ^ 1) : 0);
     }
     if (!mbar_wait(&bars[1], it & 1, abort_flag, p.status, kErrAttnBarrierTimeout, blockIdx.x)) { ok = false; break; }
     tc_fence_after();
-    if (kBufs == 1 && r == 0 && i + 1 < n_q) {    // single buffer: refill it now that every MMA reading it is done
-      mbar_expect_tx(&bars[3], 2 * kImg);
-      tma_tile<NB>(q_img0, &map_q, &bars[3], q0 + kBlk, h, b);
-      tma_tile<NB>(do_img0, &map_do, &bars[3], q0 + kBlk, h, b);
+    // every MMA that read this block's Q / dO buffer is done: refill it
+    {
+      const int nxt = kBufs == 2 ? i + 2 : i + 1;
+      if (tid == 0 && nxt < n_q) {
+        mbar_expect_tx(&bars[3 + sb], 2 * kImg);
+        tma_tile<NB>(q_img0 + sb * kImg, &map_q, &bars[3 + sb], nxt * kBlk, h, b);
+        tma_tile<NB>(do_img0 + sb * kImg, &map_do, &bars[3 + sb], nxt * kBlk, h, b);
+      }
     }
     {
       // dQ of this (query block, key block) pair: TMEM -> registers -> shared staging -> one bulk fp32
       // reduction into the [B, H, T, DP] accumulator (several key blocks add into the same query rows)
 #pragma unroll
       for (int c = 0; c < DP / 32; ++c) {
+        if ((c & 1) != half && DP > 32) continue;            // the two threads of a row share the chunks
+        if (DP == 32 && half != 0) continue;
         uint32_t raw[32];
-        tmem_ld_32x32(tmem + lane_base + c * 32, raw);
+        tmem_ld_32x32(tmem + kColDQ + lane_base + c * 32, raw);
         tmem_wait_ld();
         float4* dst = reinterpret_cast<float4*>(dq_stage + r * DP + c * 32);
 #pragma unroll
@@ -520,7 +1010,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
       fence_proxy_async();
       tc_fence_before();
       __syncthreads();
-      if (r == 0) {
+      if (tid == 0) {
         const int qvalid = min(kBlk, p.T - q0);
         float* gdst = p.dq_acc + ((static_cast<int64_t>(b) * p.H + h) * p.T + q0) * DP;
         bulk_reduce_add_f32(gdst, dq_stage, static_cast<uint32_t>(qvalid) * DP * 4);
@@ -528,7 +1018,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
       }
     }
   }
-  if (r == 0) bulk_wait_group0();
+  if (tid == 0) bulk_wait_group0();
 
   if (ok && it > 0) {
     const int key = k0 + r;
@@ -536,21 +1026,21 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
 #pragma unroll
     for (int c = 0; c < DP / 32; ++c) {
       uint32_t rv[32], rk[32];
-      tmem_ld_32x32(tmem + 256 + lane_base + c * 32, rv);
-      tmem_ld_32x32(tmem + 384 + lane_base + c * 32, rk);
+      tmem_ld_32x32(tmem + kColDV + lane_base + c * 32, rv);
+      tmem_ld_32x32(tmem + kColDK + lane_base + c * 32, rk);
       tmem_wait_ld();
       if (key < p.T) {
 #pragma unroll
         for (int j = 0; j < 32; ++j) {
           const int d = c * 32 + j;
           if (d < p.dh) {
-            dst[p.dh + d] = from_f<T>(__uint_as_float(rk[j]));
-            dst[2 * p.dh + d] = from_f<T>(__uint_as_float(rv[j]));
+            if (half == 0) dst[p.dh + d] = from_f<T>(__uint_as_float(rk[j]));
+            else dst[2 * p.dh + d] = from_f<T>(__uint_as_float(rv[j]));
           }
         }
       }
     }
-  } else if (ok && k0 + r < p.T) {
+  } else if (ok && half == 0 && k0 + r < p.T) {
     // no query block attends to this key block (cannot happen for causal / full attention, kept for safety)
     T* dst = reinterpret_cast<T*>(p.dqkv) + (static_cast<int64_t>(b) * p.T + k0 + r) * ld + h * 3 * p.dh;
     for (int d = 0; d < p.dh; ++d) { dst[p.dh + d] = from_f<T>(0.f); dst[2 * p.dh + d] = from_f<T>(0.f); }
@@ -583,7 +1073,25 @@ struct AttnMaps {
 };
 
 template <typename T, int DP>
+static void launch_fwd_ws(const AttnMaps& m, const AttnParams& p, cudaStream_t s) {
+  auto kern = attn_fwd_ws_kernel<T, DP>;
+  static bool done = false;
+  if (!done) {
+    C10_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, fwd_ws_smem<DP>()));
+    done = true;
+  }
+  const int tiles = ((p.T + kBlk - 1) / kBlk) * p.H * p.B;
+  const int sms = at::cuda::getCurrentDeviceProperties()->multiProcessorCount;
+  kern<<<std::min(tiles, sms), kWsThreads, fwd_ws_smem<DP>(), s>>>(m.q, m.k, m.v, p);
+  C10_CUDA_KERNEL_LAUNCH_CHECK();
+}
+
+template <typename T, int DP>
 static void launch_fwd(const AttnMaps& m, const AttnParams& p, cudaStream_t s) {
+  if constexpr (DP <= 64) {
+    launch_fwd_ws<T, DP>(m, p, s);
+    return;
+  }
   auto kern = attn_fwd_kernel<T, DP>;
   static bool done = false;
   if (!done) {
@@ -603,7 +1111,7 @@ static void launch_bwd(const AttnMaps& m, const AttnParams& p, cudaStream_t s) {
     done = true;
   }
   dim3 grid((p.T + kBlk - 1) / kBlk, p.H, p.B);
-  kern<<<grid, kAttnThreads, bwd_smem<DP>(), s>>>(m.q, m.k, m.v, m.d_out, p);
+  kern<<<grid, kBwdThreads, bwd_smem<DP>(), s>>>(m.q, m.k, m.v, m.d_out, p);
   C10_CUDA_KERNEL_LAUNCH_CHECK();
 }
 
@@ -631,6 +1139,7 @@ static AttnParams base_params(const torch::Tensor& qkv, bool causal, const c10::
   AttnParams p{};
   p.B = qkv.size(0); p.T = qkv.size(1); p.H = qkv.size(2); p.dh = qkv.size(3) / 3;
   p.scale = static_cast<float>(scale);
+  TORCH_CHECK(scale > 0.0, "the softmax scale must be positive");
   p.causal = causal ? 1 : 0;
   p.is_bf16 = qkv.scalar_type() == torch::kBFloat16;
   p.status = reinterpret_cast<int*>(status_ptr);
@@ -686,8 +1195,12 @@ bool attention_ready() { return true; }
 // Returns (out, lse, packed): `packed` is the padded QKV copy when one was needed (undefined otherwise); the
 // backward takes it back so the copy is made once.
 std::vector<torch::Tensor> attention_fwd(torch::Tensor qkv, bool causal, c10::optional<torch::Tensor> key_bias,
-                                         double scale, int64_t status_ptr) {
+                                         double scale, int64_t status_ptr, c10::optional<torch::Tensor> trace) {
   AttnParams p = base_params(qkv, causal, key_bias, scale, status_ptr);
+  if (trace.has_value() && trace->defined()) {
+    TORCH_CHECK(trace->scalar_type() == torch::kInt64 && trace->numel() >= 2 * 4096 * 2 && trace->is_cuda());
+    p.trace = reinterpret_cast<long long*>(trace->data_ptr<int64_t>());
+  }
   auto out = torch::empty({p.B, p.T, p.H, p.dh}, qkv.options());
   auto lse = torch::empty({p.B, p.H, p.T}, qkv.options().dtype(torch::kFloat32));
   torch::Tensor packed;

@@ -38,7 +38,7 @@ torch::Tensor multi_sumsq(std::vector<torch::Tensor> grads, std::vector<double> 
 void multi_scale(std::vector<torch::Tensor> grads, torch::Tensor coef);
 // attention_sm100.cu
 std::vector<torch::Tensor> attention_fwd(torch::Tensor qkv, bool causal, c10::optional<torch::Tensor> key_bias,
-                                         double scale, int64_t status_ptr);
+                                         double scale, int64_t status_ptr, c10::optional<torch::Tensor> trace);
 torch::Tensor attention_bwd(torch::Tensor dout, torch::Tensor qkv, torch::Tensor out, torch::Tensor lse, bool causal,
                             c10::optional<torch::Tensor> key_bias, double scale, int64_t status_ptr,
                             c10::optional<torch::Tensor> packed);

@@ -237,9 +237,12 @@ def multi_sgd(params, grads, bufs, shadows, lr, momentum, wd, first, grad_scale)
     require().multi_sgd(params, grads, bufs, shadows, float(lr), float(momentum), float(wd), bool(first), grad_scale)
 
 
+ATTN_TRACE = None   # optional int64 [2, 4096, 2] CUDA tensor: event stamps of CTA 0 of the next attention forward launches
+
+
 def attention_fwd(qkv, causal, key_bias, scale):
     m = require()
-    out, lse, packed = m.attention_fwd(qkv, bool(causal), key_bias, float(scale), m.status_device_ptr())
+    out, lse, packed = m.attention_fwd(qkv, bool(causal), key_bias, float(scale), m.status_device_ptr(), ATTN_TRACE)
     _count(1 if packed is None else 2)
     return out, (lse, packed)
 
