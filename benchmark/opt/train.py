@@ -1,8 +1,9 @@
 """OPT training entry point: ``torchrun --nproc_per_node N benchmark/opt/train.py -m opt_13b --tp 3d --tp_size 8 --ckpt ...``
 
 Parity: benchmark/opt/train.py + opt.py:536-653.  The reference optimiser for OPT is SGD (opt.py:623); ``--optimizer
-adamw`` switches.  ``--fsdp`` / ``-O3`` of the reference are not offered (data parallelism is the package's own
-bucketed wrapper; parameters stay fp32 masters with 16-bit shadows).
+adamw`` switches.  ``--fsdp`` shards parameters, gradients and optimizer state over the data-parallel group with the
+package's own wrapper (``cubework_b200.parallel.fsdp``), one unit per decoder layer as in opt.py:544-562; the
+reference's ``-O3`` (fairscale loss scaling) has no counterpart because bf16 needs no loss scaling.
 """
 import os
 import sys

@@ -74,6 +74,12 @@ def shadow(param: torch.Tensor, dtype: torch.dtype) -> torch.Tensor:
     return s.tensor
 
 
+def drop_shadow(param: torch.Tensor):
+    """Forget the cached low-precision copies of ``param`` (its storage was replaced, or is about to be freed)."""
+    for key in [k for k in _SHADOWS if k[0] == id(param)]:
+        _SHADOWS.pop(key, None)
+
+
 def peek_shadow(param: torch.Tensor, dtype: torch.dtype):
     s = _SHADOWS.get((id(param), dtype))
     return s

@@ -340,9 +340,17 @@ template <bool MASKED, bool BIAS>
 __device__ __forceinline__ float chunk_max(const uint32_t (&raw)[32], const float* bias, float sc2, int key0, int q_idx, int T,
                                            bool causal, float m) {
   float mm[4] = {m, -INFINITY, -INFINITY, -INFINITY};      // four chains: the maximum is not one long dependency
+  float bv[32];
+  if (BIAS) {
+#pragma unroll
+    for (int q = 0; q < 8; ++q) {                           // eight 16-byte broadcast loads instead of 32 scalar ones
+      const float4 t = reinterpret_cast<const float4*>(bias)[q];
+      bv[q * 4] = t.x; bv[q * 4 + 1] = t.y; bv[q * 4 + 2] = t.z; bv[q * 4 + 3] = t.w;
+    }
+  }
 #pragma unroll
   for (int i = 0; i < 32; ++i) {
-    float sx = BIAS ? fmaf(__uint_as_float(raw[i]), sc2, bias[i]) : __uint_as_float(raw[i]);
+    float sx = BIAS ? fmaf(__uint_as_float(raw[i]), sc2, bv[i]) : __uint_as_float(raw[i]);
     if (MASKED) {
       const int key = key0 + i;
       if (key >= T || (causal && key > q_idx)) sx = -INFINITY;
@@ -356,9 +364,17 @@ template <bool MASKED, bool BIAS>
 __device__ __forceinline__ float chunk_exp(const uint32_t (&raw)[32], const float* bias, float sc2, float m_use, int key0,
                                            int q_idx, int T, bool causal, float (&pv)[32]) {
   float ll[4] = {0.f, 0.f, 0.f, 0.f};
+  float bv[32];
+  if (BIAS) {
+#pragma unroll
+    for (int q = 0; q < 8; ++q) {
+      const float4 t = reinterpret_cast<const float4*>(bias)[q];
+      bv[q * 4] = t.x; bv[q * 4 + 1] = t.y; bv[q * 4 + 2] = t.z; bv[q * 4 + 3] = t.w;
+    }
+  }
 #pragma unroll
   for (int i = 0; i < 32; ++i) {
-    float e = ex2_approx(fmaf(__uint_as_float(raw[i]), sc2, BIAS ? bias[i] - m_use : -m_use));
+    float e = ex2_approx(fmaf(__uint_as_float(raw[i]), sc2, BIAS ? bv[i] - m_use : -m_use));
     if (MASKED) {
       const int key = key0 + i;
       if (key >= T || (causal && key > q_idx)) e = 0.f;
@@ -373,14 +389,15 @@ constexpr int kWsThreads = 384;
 constexpr int kWsKRing = 2, kWsBiasRing = 4;
 template <int DP>
 constexpr int fwd_ws_smem() {
-  return 2 * ((1 + kWsKRing + 1) * kBlk * 128 + 2 * kBlk * 128 + kWsBiasRing * kBlk * 4) + 512 + 1024;
+  return 2 * ((1 + kWsKRing + 1) * kBlk * 128 + 2 * kBlk * 128 + kWsBiasRing * kBlk * 4) + 768 + 1024;
 }
 
 struct WsLaneBars {
   uint64_t q_full, q_empty;
   uint64_t k_full[kWsKRing], k_empty[kWsKRing];
   uint64_t v_full, v_empty;
-  uint64_t s_full, p_ready, o_full;
+  uint64_t s_full, s_free, p_ready, o_full;
+  int bias_nz[kWsBiasRing];        // the key bias of this ring slot has a non-zero entry
 };
 
 template <typename T, int DP>
@@ -404,7 +421,7 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
       mbar_init(&bb->q_full, 1); mbar_init(&bb->q_empty, 1);
       for (int i = 0; i < kWsKRing; ++i) { mbar_init(&bb->k_full[i], 1); mbar_init(&bb->k_empty[i], 1); }
       mbar_init(&bb->v_full, 1); mbar_init(&bb->v_empty, 1);
-      mbar_init(&bb->s_full, 1); mbar_init(&bb->p_ready, kBlk); mbar_init(&bb->o_full, 1);
+      mbar_init(&bb->s_full, 1); mbar_init(&bb->s_free, kBlk); mbar_init(&bb->p_ready, kBlk); mbar_init(&bb->o_full, 1);
     }
     *abort_flag = 0;
     fence_barrier_init();
@@ -433,7 +450,6 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
   const int n_qb = (p.T + kBlk - 1) / kBlk;
   const int bh_total = p.B * p.H;
   const int tiles = n_qb * bh_total;
-  const bool has_bias = p.key_bias != nullptr;
   auto n_kv_of = [&](int qb) { return p.causal ? min(n_qb, qb + 1) : n_qb; };
   // tiles of this lane, heaviest (most key blocks) first: t = first, first + stride, ...
   const int first = blockIdx.x + w * gridDim.x, stride = 2 * gridDim.x;
@@ -460,13 +476,17 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
           ok = ok && mbar_wait(&bars->k_empty[ks], ((kcount / kWsKRing) & 1) ^ 1, abort_flag, p.status, kErrAttnBarrierTimeout, t);
         ok = __shfl_sync(0xffffffffu, ok, 0);
         if (!ok) break;
-        if (has_bias) {
+        if (p.key_bias != nullptr) {
           float* dst = s_bias + (kcount % kWsBiasRing) * kBlk;
 #pragma unroll
           for (int i = 0; i < 4; ++i) {
             const int key = j * kBlk + lane * 4 + i;
             dst[lane * 4 + i] = key < p.T ? p.key_bias[static_cast<int64_t>(b) * p.T + key] * kLog2e : 0.f;
           }
+          // an all-zero bias (no padding in this key block) lets the softmax warps skip it
+          const bool nz = dst[lane * 4] != 0.f || dst[lane * 4 + 1] != 0.f || dst[lane * 4 + 2] != 0.f || dst[lane * 4 + 3] != 0.f;
+          const bool any_nz = __any_sync(0xffffffffu, nz);
+          if (lane == 0) bars->bias_nz[kcount % kWsBiasRing] = any_nz ? 1 : 0;
           __threadfence_block();
         }
         __syncwarp();
@@ -489,7 +509,7 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
     if (lane == 0) {
       const uint32_t idesc_s = make_idesc_f16(kBlk, kBlk, false, false, p.is_bf16);
       const uint32_t idesc_o = make_idesc_f16(kBlk, DP, false, true, p.is_bf16);
-      int kcount = 0, vcount = 0, pcount = 0, tile_it = 0;
+      int kcount = 0, vcount = 0, pcount = 0, fcount = 0, tile_it = 0;
       bool ok = true;
       auto issue_s = [&](bool last) -> bool {
         const int ks = kcount % kWsKRing;
@@ -510,6 +530,15 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
         ok = mbar_wait(&bars->q_full, tile_it & 1, abort_flag, p.status, kErrAttnBarrierTimeout, t);
         ok = ok && issue_s(n_kv == 1);
         for (int j = 0; j < n_kv && ok; ++j) {
+          // the group has read S_j for the last time: S_{j+1} goes first, it is what the group needs soonest
+          ok = mbar_wait(&bars->s_free, fcount & 1, abort_flag, p.status, kErrAttnBarrierTimeout, t);
+          if (!ok) break;
+          ++fcount;
+          if (j + 1 < n_kv) {
+            tc_fence_after();
+            ok = issue_s(j + 1 == n_kv - 1);
+            if (!ok) break;
+          }
           ok = mbar_wait(&bars->p_ready, pcount & 1, abort_flag, p.status, kErrAttnBarrierTimeout, t);
           if (!ok) break;
           ++pcount;
@@ -523,7 +552,6 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
           tc_commit(&bars->v_empty);
           tc_commit(&bars->o_full);
           ++vcount;
-          if (j + 1 < n_kv) ok = issue_s(j + 1 == n_kv - 1);
         }
       }
     }
@@ -553,6 +581,7 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
         const bool tail = k0 + kBlk > p.T;
         const bool cdiag = p.causal && j == qb;
         const float* bias_j = s_bias + ((kbase + j) % kWsBiasRing) * kBlk;
+        const bool has_bias = p.key_bias != nullptr && bars->bias_nz[(kbase + j) % kWsBiasRing] != 0;
         const uint32_t s_addr = tm_s + lane_base;
         uint32_t ra[32], rb[32];
         float m_blk = -INFINITY;
@@ -640,6 +669,8 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
           tmem_ld_32x32(s_addr + 96, ra);
           CW_EXP_STEP(rb, 1)
           tmem_wait_ld_for(ra);
+          tc_fence_before();
+          mbar_arrive(&bars->s_free);                 // last read of the scores: the next block's S may overwrite them
           CW_EXP_STEP(rc, 2)
           CW_EXP_STEP(ra, 3)
 #undef CW_EXP_STEP
@@ -662,6 +693,8 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
             }
             store_p_chunk<T>(p_img, r, c * 32, pv);
           }
+          tc_fence_before();
+          mbar_arrive(&bars->s_free);
         }
         l_run = l_run * alpha + l_blk;
         attn_trace(tr, 0, ntr, 6);
@@ -705,8 +738,16 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
         T* o = reinterpret_cast<T*>(p.out) + ((static_cast<int64_t>(b) * p.T + row0) * p.H + h) * p.dh;
         const int64_t row_pitch = static_cast<int64_t>(p.H) * p.dh;
         const int rows = min(32, p.T - row0);
-        for (int rr = 0; rr < rows; ++rr)
-          for (int d = lane; d < p.dh; d += 32) o[rr * row_pitch + d] = stage[rr * DP + d];
+        for (int d = lane; d < p.dh; d += 32) {
+          for (int r0 = 0; r0 < rows; r0 += 8) {
+            T v[8];
+#pragma unroll
+            for (int u = 0; u < 8; ++u) v[u] = stage[min(r0 + u, 31) * DP + d];
+#pragma unroll
+            for (int u = 0; u < 8; ++u)
+              if (r0 + u < rows) o[(r0 + u) * row_pitch + d] = v[u];
+          }
+        }
         __syncwarp();
       }
       attn_trace(tr, 0, ntr, 9);
@@ -785,9 +826,17 @@ __device__ __forceinline__ void bwd_chunk(const uint32_t (&rs)[32], const uint32
                                           float lse2, float scale, float nds, int key0, int q_idx, int Tn, bool causal,
                                           uint8_t* p_img, uint8_t* ds_img, int r, int c0) {
   float pv[32], dsv[32];
+  float bv[32];
+  if (BIAS) {
+#pragma unroll
+    for (int q = 0; q < 8; ++q) {
+      const float4 t = reinterpret_cast<const float4*>(bias)[q];
+      bv[q * 4] = t.x; bv[q * 4 + 1] = t.y; bv[q * 4 + 2] = t.z; bv[q * 4 + 3] = t.w;
+    }
+  }
 #pragma unroll
   for (int j = 0; j < 32; ++j) {
-    float pr = ex2_approx(fmaf(__uint_as_float(rs[j]), sc2, BIAS ? bias[j] - lse2 : -lse2));
+    float pr = ex2_approx(fmaf(__uint_as_float(rs[j]), sc2, BIAS ? bv[j] - lse2 : -lse2));
     if (MASKED) {
       const int key = key0 + j;
       if (key >= Tn || q_idx >= Tn || (causal && key > q_idx)) pr = 0.f;
@@ -835,8 +884,11 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
   const int k0 = kb * kBlk;
   const int64_t ld = static_cast<int64_t>(p.H) * 3 * p.dh;
   const float* kbias = p.key_bias != nullptr ? p.key_bias + static_cast<int64_t>(b) * p.T : nullptr;
-  const bool has_bias = kbias != nullptr;
-  if (has_bias && tid < kBlk) s_bias[tid] = k0 + tid < p.T ? kbias[k0 + tid] * kLog2e : 0.f;
+  int bias_nz = 0;                                  // this thread's bias entry is non-zero
+  if (kbias != nullptr && tid < kBlk) {
+    s_bias[tid] = k0 + tid < p.T ? kbias[k0 + tid] * kLog2e : 0.f;
+    bias_nz = s_bias[tid] != 0.f;
+  }
   const int n_q = (p.T + kBlk - 1) / kBlk;
   const int i0 = p.causal ? kb : 0;
 
@@ -864,7 +916,8 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
     tmem_relinquish();
   }
   tc_fence_before();
-  __syncthreads();
+  // an all-zero bias (no padding among these keys) is skipped altogether
+  const bool has_bias = __syncthreads_or(bias_nz) != 0;
   tc_fence_after();
   const uint32_t tmem = *tmem_slot;
   const uint32_t lane_base = static_cast<uint32_t>((warp & 3) * 32) << 16;

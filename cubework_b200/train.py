@@ -49,6 +49,8 @@ def get_parser(description, default_model, token_unit="tokens"):
     p.add_argument("--save_dir", default=None, help="write a sharded checkpoint at the end of every epoch")
     p.add_argument("--resume_step", type=int, default=None)
     p.add_argument("--dropout", type=float, default=None)
+    p.add_argument("--fsdp", action="store_true",
+                   help="shard parameters, gradients and optimizer state over the data-parallel group (one unit per block)")
     p.set_defaults(token_unit=token_unit)
     return p
 
@@ -97,7 +99,11 @@ def run(args, family):
     dev = get_current_device()
     model, criterion, metric, make_batch, tokens_per_sample = family.build(args)
     model = model.to(dev)
-    if pm.DATA.world_size > 1:
+    if getattr(args, "fsdp", False):
+        from cubework_b200.models import gpt2 as _g, opt as _o, vit as _v
+        from cubework_b200.parallel.fsdp import FullyShardedDataParallel
+        model = FullyShardedDataParallel(model, unit_classes=(_g.GPT2Block, _o.OPTDecoderLayer, _v.ViTBlock))
+    elif pm.DATA.world_size > 1:
         model = DataParallel(model)
     numel, numel_local = calc_model_size(model)
     logger.info(f"model {args.model_name}: {numel / 1e6:.1f} M parameters ({numel_local / 1e6:.1f} M on this rank)")
