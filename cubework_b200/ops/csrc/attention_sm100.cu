@@ -768,7 +768,7 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
 }
 
 // Copy `parts` consecutive [dh] slices per (token, head) of src [B, T, H, parts*dh] into zero-padded rows
-// dst [parts][B, H, T, W] (W a multiple of 64): makes every row 16-byte aligned for TMA.
+// dst [parts][B, H, T, W] (W a multiple of 8 elements): makes every row 16-byte aligned for TMA.
 template <typename T>
 __global__ void attn_pack_kernel(const T* __restrict__ src, T* __restrict__ dst, int B, int Tn, int H, int dh, int parts,
                                  int W) {
@@ -857,8 +857,9 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
   constexpr int NB = (DP + 63) / 64;
   constexpr int kImg = NB * kBlk * 128;
   constexpr uint32_t kTmemCols = 512;
-  // TMEM columns.  DP <= 64: S [0,128) dP [128,256) dV [256,..) dK [320,..) dQ [384,..): dQ has columns of its own, so
-  // the scores of the next query block are multiplied while this block's dQ is being written out.
+  // TMEM columns.  DP <= 64: S [0,128) dP [128,256) dV [256,..) dK [320,..) dQ [384,..) and [448,..): dQ has two
+  // column sets of its own, used alternately, so the scores of the next query block are multiplied right behind this
+  // block's products and a block's dQ is written out one iteration later, while the next products run.
   // DP > 64: S/dQ [0,128) dP [128,256) dV [256,..) dK [384,..) (dQ reuses the score columns).
   constexpr bool kSep = DP <= 64;
   constexpr uint32_t kColDV = 256, kColDK = kSep ? 320 : 384, kColDQ = kSep ? 384 : 0;
@@ -871,11 +872,13 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
   uint8_t* do_img0 = q_img0 + kBufs * kImg;
   uint8_t* p_img = do_img0 + kBufs * kImg;
   uint8_t* ds_img = p_img + 2 * kBlk * 128;
-  uint64_t* bars = reinterpret_cast<uint64_t*>(ds_img + 2 * kBlk * 128);   // 0: S,dP  1: dV,dK,dQ  2: K,V  3,4: Q,dO
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 5);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(ds_img + 2 * kBlk * 128);   // 0: S,dP  1: dQ  2: K,V  3,4: Q,dO  5: dV,dK
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 6);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
-  float* s_bias = reinterpret_cast<float*>(tmem_slot + 2);                 // [128] key bias (log2 domain) of this block
-  float* dq_stage = reinterpret_cast<float*>(p_img);                       // [128][DP] fp32, aliases P / dS between uses
+  float* s_bias = reinterpret_cast<float*>(tmem_slot + 4);                 // [128] key bias (log2 domain) of this block
+  // [128][DP] fp32 staging of dQ: a region of its own for DP <= 64 (it is filled while the MMAs still read P / dS),
+  // otherwise it aliases P / dS between their uses
+  float* dq_stage = kSep ? s_bias + kBlk : reinterpret_cast<float*>(p_img);
 
   const int tid = threadIdx.x, warp = tid >> 5;
   const int r = tid & 127;                         // query row inside a block == TMEM lane
@@ -893,7 +896,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
   const int i0 = p.causal ? kb : 0;
 
   if (tid == 0) {
-    for (int i = 0; i < 5; ++i) mbar_init(&bars[i], 1);
+    for (int i = 0; i < 6; ++i) mbar_init(&bars[i], 1);
     *abort_flag = 0;
     fence_barrier_init();
     mbar_expect_tx(&bars[2], 2 * kImg);
@@ -946,7 +949,8 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
   };
 
   bool ok = true;
-  int it = 0;
+  int it = 0, ntr = 0;
+  const bool trb = tid == 0 && blockIdx.y == 0 && blockIdx.z == 0;
   if (kSep && tid == 0 && i0 < n_q) issue_scores(0, 0);
   for (int i = i0; i < n_q && ok; ++i, ++it) {
     const int q0 = i * kBlk;
@@ -957,14 +961,18 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
     const int64_t stat = (static_cast<int64_t>(b) * p.H + h) * p.T + q_idx;
     const float lse2 = q_idx < p.T ? p.lse[stat] : 0.f;
     const float nds = q_idx < p.T ? -p.delta[stat] * p.scale : 0.f;
-    // every thread has finished reading dQ of the previous query block, and the bulk reduction of that block has
-    // finished reading its staging area (aliased with P / dS)
-    if (tid == 0) bulk_wait_group_read0();
-    tc_fence_before();
-    __syncthreads();
-    if (!kSep && tid == 0) issue_scores(it, sb);
+    if (!kSep) {
+      // every thread has finished reading dQ of the previous query block, and the bulk reduction of that block has
+      // finished reading its staging area (aliased with P / dS)
+      if (tid == 0) bulk_wait_group_read0();
+      tc_fence_before();
+      __syncthreads();
+      if (tid == 0) issue_scores(it, sb);
+    }
+    if (trb) attn_trace(p.trace, 0, ntr, 1);
     if (!mbar_wait(&bars[0], it & 1, abort_flag, p.status, kErrAttnBarrierTimeout, blockIdx.x)) { ok = false; break; }
     tc_fence_after();
+    if (trb) attn_trace(p.trace, 0, ntr, 2);
     const bool tail = (k0 + kBlk > p.T) || (q0 + kBlk > p.T);
     const bool cdiag = p.causal && i == kb;
     const int wq = warp & 3;                       // this warp's 32-row block
@@ -1012,48 +1020,21 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
         }
       }
     }
+    if (trb) attn_trace(p.trace, 0, ntr, 3);
     fence_proxy_async();
     tc_fence_before();
     __syncthreads();
-    if (tid == 0) {
-      tc_fence_after();
-      const uint32_t acc = it > 0 ? 1u : 0u;
-#pragma unroll
-      for (int k16 = 0; k16 < kBlk / 16; ++k16)   // dQ[q, d] = sum_key dS[q, key] K[key, d]
-        tc_mma_f16(tmem + kColDQ, kmajor_desc(smem_u32(ds_img), k16), mnmajor_desc(smem_u32(k_img), k16), idesc_dq, k16 > 0);
-#pragma unroll
-      for (int k16 = 0; k16 < kBlk / 16; ++k16)   // dV[key, d] += sum_q P[q, key] dO[q, d]
-        tc_mma_f16(tmem + kColDV, mnmajor_desc(smem_u32(p_img), k16), mnmajor_desc(smem_u32(do_img), k16), idesc_tt,
-                   (k16 > 0) ? 1u : acc);
-#pragma unroll
-      for (int k16 = 0; k16 < kBlk / 16; ++k16)   // dK[key, d] += sum_q dS[q, key] Q[q, d]
-        tc_mma_f16(tmem + kColDK, mnmajor_desc(smem_u32(ds_img), k16), mnmajor_desc(smem_u32(q_img), k16), idesc_tt,
-                   (k16 > 0) ? 1u : acc);
-      tc_commit(&bars[1]);
-      // the scores of the next query block, behind this block's dQ write-out
-      if (kSep && i + 1 < n_q) issue_scores(it + 1, kBufs == 2 ? (sb ^ 1) : 0);
-    }
-    if (!mbar_wait(&bars[1], it & 1, abort_flag, p.status, kErrAttnBarrierTimeout, blockIdx.x)) { ok = false; break; }
-    tc_fence_after();
-    // every MMA that read this block's Q / dO buffer is done: refill it
-    {
-      const int nxt = kBufs == 2 ? i + 2 : i + 1;
-      if (tid == 0 && nxt < n_q) {
-        mbar_expect_tx(&bars[3 + sb], 2 * kImg);
-        tma_tile<NB>(q_img0 + sb * kImg, &map_q, &bars[3 + sb], nxt * kBlk, h, b);
-        tma_tile<NB>(do_img0 + sb * kImg, &map_do, &bars[3 + sb], nxt * kBlk, h, b);
-      }
-    }
-    {
-      // dQ of this (query block, key block) pair: TMEM -> registers -> shared staging -> one bulk fp32
-      // reduction into the [B, H, T, DP] accumulator (several key blocks add into the same query rows)
+    if (trb) attn_trace(p.trace, 0, ntr, 4);
+    // dQ of (query block, key block): TMEM -> registers -> shared staging -> one bulk fp32 reduction into the
+    // [B, H, T, DP] accumulator (several key blocks add into the same query rows)
+    auto drain_dq = [&](uint32_t col, int q_first) {
 #pragma unroll
       for (int c = 0; c < DP / 32; ++c) {
         if ((c & 1) != half && DP > 32) continue;            // the two threads of a row share the chunks
         if (DP == 32 && half != 0) continue;
         uint32_t raw[32];
-        tmem_ld_32x32(tmem + kColDQ + lane_base + c * 32, raw);
-        tmem_wait_ld();
+        tmem_ld_32x32(tmem + col + lane_base + c * 32, raw);
+        tmem_wait_ld_for(raw);
         float4* dst = reinterpret_cast<float4*>(dq_stage + r * DP + c * 32);
 #pragma unroll
         for (int j = 0; j < 8; ++j)
@@ -1064,33 +1045,126 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
       tc_fence_before();
       __syncthreads();
       if (tid == 0) {
-        const int qvalid = min(kBlk, p.T - q0);
-        float* gdst = p.dq_acc + ((static_cast<int64_t>(b) * p.H + h) * p.T + q0) * DP;
+        const int qvalid = min(kBlk, p.T - q_first);
+        float* gdst = p.dq_acc + ((static_cast<int64_t>(b) * p.H + h) * p.T + q_first) * DP;
+        bulk_reduce_add_f32(gdst, dq_stage, static_cast<uint32_t>(qvalid) * DP * 4);
+        bulk_commit_group();
+      }
+    };
+    const uint32_t col_dq = kSep ? kColDQ + (it & 1) * 64 : kColDQ;
+    if (tid == 0) {
+      tc_fence_after();
+      const uint32_t acc = it > 0 ? 1u : 0u;
+#pragma unroll
+      for (int k16 = 0; k16 < kBlk / 16; ++k16)   // dQ[q, d] = sum_key dS[q, key] K[key, d]
+        tc_mma_f16(tmem + col_dq, kmajor_desc(smem_u32(ds_img), k16), mnmajor_desc(smem_u32(k_img), k16), idesc_dq, k16 > 0);
+      tc_commit(&bars[1]);
+      // the scores of the next query block, right behind this block's products
+      if (kSep && i + 1 < n_q) issue_scores(it + 1, kBufs == 2 ? (sb ^ 1) : 0);
+    } else if (tid == kBlk) {
+      // a thread of another warp issues the other two products at the same time (issuing takes about a microsecond)
+      tc_fence_after();
+      const uint32_t acc = it > 0 ? 1u : 0u;
+#pragma unroll
+      for (int k16 = 0; k16 < kBlk / 16; ++k16)   // dV[key, d] += sum_q P[q, key] dO[q, d]
+        tc_mma_f16(tmem + kColDV, mnmajor_desc(smem_u32(p_img), k16), mnmajor_desc(smem_u32(do_img), k16), idesc_tt,
+                   (k16 > 0) ? 1u : acc);
+#pragma unroll
+      for (int k16 = 0; k16 < kBlk / 16; ++k16)   // dK[key, d] += sum_q dS[q, key] Q[q, d]
+        tc_mma_f16(tmem + kColDK, mnmajor_desc(smem_u32(ds_img), k16), mnmajor_desc(smem_u32(q_img), k16), idesc_tt,
+                   (k16 > 0) ? 1u : acc);
+      tc_commit(&bars[5]);
+    }
+    if (trb) attn_trace(p.trace, 0, ntr, 5);
+    if (kSep && it > 0) {
+      // while those run: write out the previous block's dQ (its MMAs were waited for at the end of that iteration)
+      if (tid == 0) bulk_wait_group_read0();               // the staging area has been read by the reduction before it
+      __syncthreads();
+      drain_dq(kColDQ + ((it - 1) & 1) * 64, q0 - kBlk);
+    }
+    if (trb) attn_trace(p.trace, 0, ntr, 6);
+    if (!mbar_wait(&bars[1], it & 1, abort_flag, p.status, kErrAttnBarrierTimeout, blockIdx.x) ||
+        !mbar_wait(&bars[5], it & 1, abort_flag, p.status, kErrAttnBarrierTimeout, blockIdx.x)) { ok = false; break; }
+    tc_fence_after();
+    if (trb) attn_trace(p.trace, 0, ntr, 7);
+    // every MMA that read this block's Q / dO buffer (and P / dS) is done: refill the buffer
+    {
+      const int nxt = kBufs == 2 ? i + 2 : i + 1;
+      if (tid == 0 && nxt < n_q) {
+        mbar_expect_tx(&bars[3 + sb], 2 * kImg);
+        tma_tile<NB>(q_img0 + sb * kImg, &map_q, &bars[3 + sb], nxt * kBlk, h, b);
+        tma_tile<NB>(do_img0 + sb * kImg, &map_do, &bars[3 + sb], nxt * kBlk, h, b);
+      }
+    }
+    if (!kSep) drain_dq(kColDQ, q0);
+  }
+  if (kSep && ok && it > 0) {
+    // the last block's dQ
+    const int q_last = (i0 + it - 1) * kBlk;
+    if (tid == 0) bulk_wait_group_read0();
+    __syncthreads();
+    {
+#pragma unroll
+      for (int c = 0; c < DP / 32; ++c) {
+        if ((c & 1) != half && DP > 32) continue;
+        if (DP == 32 && half != 0) continue;
+        uint32_t raw[32];
+        tmem_ld_32x32(tmem + kColDQ + ((it - 1) & 1) * 64 + lane_base + c * 32, raw);
+        tmem_wait_ld_for(raw);
+        float4* dst = reinterpret_cast<float4*>(dq_stage + r * DP + c * 32);
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+          dst[j] = make_float4(__uint_as_float(raw[4 * j]), __uint_as_float(raw[4 * j + 1]),
+                               __uint_as_float(raw[4 * j + 2]), __uint_as_float(raw[4 * j + 3]));
+      }
+      fence_proxy_async();
+      tc_fence_before();
+      __syncthreads();
+      if (tid == 0) {
+        const int qvalid = min(kBlk, p.T - q_last);
+        float* gdst = p.dq_acc + ((static_cast<int64_t>(b) * p.H + h) * p.T + q_last) * DP;
         bulk_reduce_add_f32(gdst, dq_stage, static_cast<uint32_t>(qvalid) * DP * 4);
         bulk_commit_group();
       }
     }
   }
   if (tid == 0) bulk_wait_group0();
+  __syncthreads();          // the last reduction has read its staging area, which the rows below may reuse
 
   if (ok && it > 0) {
-    const int key = k0 + r;
-    T* dst = reinterpret_cast<T*>(p.dqkv) + (static_cast<int64_t>(b) * p.T + min(key, p.T - 1)) * ld + h * 3 * p.dh;
+    // dK (threads of half 0) and dV (half 1): rows go through shared memory (P / dS are free now) so that each global
+    // store instruction writes one row's contiguous bytes instead of one column of 32 rows that lie kilobytes apart
+    const int wq = warp & 3, lane = tid & 31;
+    T* stage = reinterpret_cast<T*>(half == 0 ? p_img : ds_img) + wq * 32 * DP;      // this warp's [32][DP]
+    const uint32_t col = half == 0 ? kColDK : kColDV;
 #pragma unroll
     for (int c = 0; c < DP / 32; ++c) {
-      uint32_t rv[32], rk[32];
-      tmem_ld_32x32(tmem + kColDV + lane_base + c * 32, rv);
-      tmem_ld_32x32(tmem + kColDK + lane_base + c * 32, rk);
-      tmem_wait_ld();
-      if (key < p.T) {
+      uint32_t raw[32];
+      tmem_ld_32x32(tmem + col + lane_base + c * 32, raw);
+      tmem_wait_ld_for(raw);
+      uint4* d4 = reinterpret_cast<uint4*>(stage + lane * DP + c * 32);
 #pragma unroll
-        for (int j = 0; j < 32; ++j) {
-          const int d = c * 32 + j;
-          if (d < p.dh) {
-            if (half == 0) dst[p.dh + d] = from_f<T>(__uint_as_float(rk[j]));
-            else dst[2 * p.dh + d] = from_f<T>(__uint_as_float(rv[j]));
-          }
-        }
+      for (int q = 0; q < 4; ++q) {
+        uint4 u;
+        u.x = pack_pair<T>(__uint_as_float(raw[q * 8 + 0]), __uint_as_float(raw[q * 8 + 1]));
+        u.y = pack_pair<T>(__uint_as_float(raw[q * 8 + 2]), __uint_as_float(raw[q * 8 + 3]));
+        u.z = pack_pair<T>(__uint_as_float(raw[q * 8 + 4]), __uint_as_float(raw[q * 8 + 5]));
+        u.w = pack_pair<T>(__uint_as_float(raw[q * 8 + 6]), __uint_as_float(raw[q * 8 + 7]));
+        d4[q] = u;
+      }
+    }
+    __syncwarp();
+    const int row0 = k0 + wq * 32;
+    const int rows = min(32, p.T - row0);
+    T* dst = reinterpret_cast<T*>(p.dqkv) + (static_cast<int64_t>(b) * p.T + row0) * ld + h * 3 * p.dh + (half == 0 ? p.dh : 2 * p.dh);
+    for (int d = lane; d < p.dh; d += 32) {
+      for (int r0 = 0; r0 < rows; r0 += 8) {
+        T v[8];
+#pragma unroll
+        for (int u = 0; u < 8; ++u) v[u] = stage[min(r0 + u, 31) * DP + d];
+#pragma unroll
+        for (int u = 0; u < 8; ++u)
+          if (r0 + u < rows) dst[(r0 + u) * ld + d] = v[u];
       }
     }
   } else if (ok && half == 0 && k0 + r < p.T) {
@@ -1118,7 +1192,8 @@ template <int DP>
 constexpr int fwd_smem() { return 3 * ((DP + 63) / 64) * kBlk * 128 + 2 * kBlk * 128 + 64 + 1024 + 1024; }
 template <int DP>
 constexpr int bwd_smem() {
-  return (DP <= 64 ? 6 : 4) * ((DP + 63) / 64) * kBlk * 128 + 4 * kBlk * 128 + 64 + 1024 + 512;
+  return (DP <= 64 ? 6 : 4) * ((DP + 63) / 64) * kBlk * 128 + 4 * kBlk * 128 + 64 + 1024 + 512 +
+         (DP <= 64 ? kBlk * DP * 4 : 0);
 }
 
 struct AttnMaps {
@@ -1204,7 +1279,9 @@ static AttnParams base_params(const torch::Tensor& qkv, bool causal, const c10::
   return p;
 }
 
-static int pack_width(int dh) { return dh <= 64 ? 64 : 128; }
+// Row width of the padded copy: the TMA box is 64 columns wide whatever the tensor's extent (columns past the extent are
+// zero-filled), so a narrow head only needs its rows 16-byte aligned.
+static int pack_width(int dh) { return dh <= 32 ? 32 : dh <= 64 ? 64 : 128; }
 
 // [parts][B, H, T, W] zero-padded copy of src [B, T, H, parts*dh].
 static torch::Tensor pack_heads(const torch::Tensor& src, int B, int T, int H, int dh, int parts, cudaStream_t stream) {
@@ -1270,8 +1347,12 @@ std::vector<torch::Tensor> attention_fwd(torch::Tensor qkv, bool causal, c10::op
 
 torch::Tensor attention_bwd(torch::Tensor dout, torch::Tensor qkv, torch::Tensor out, torch::Tensor lse, bool causal,
                             c10::optional<torch::Tensor> key_bias, double scale, int64_t status_ptr,
-                            c10::optional<torch::Tensor> packed_opt) {
+                            c10::optional<torch::Tensor> packed_opt, c10::optional<torch::Tensor> trace) {
   AttnParams p = base_params(qkv, causal, key_bias, scale, status_ptr);
+  if (trace.has_value() && trace->defined()) {
+    TORCH_CHECK(trace->scalar_type() == torch::kInt64 && trace->numel() >= 2 * 4096 * 2 && trace->is_cuda());
+    p.trace = reinterpret_cast<long long*>(trace->data_ptr<int64_t>());
+  }
   TORCH_CHECK(dout.is_contiguous() && dout.numel() == out.numel() && dout.scalar_type() == qkv.scalar_type());
   auto dqkv = torch::empty_like(qkv);
   if (qkv.numel() == 0) return dqkv;

@@ -41,7 +41,7 @@ std::vector<torch::Tensor> attention_fwd(torch::Tensor qkv, bool causal, c10::op
                                          double scale, int64_t status_ptr, c10::optional<torch::Tensor> trace);
 torch::Tensor attention_bwd(torch::Tensor dout, torch::Tensor qkv, torch::Tensor out, torch::Tensor lse, bool causal,
                             c10::optional<torch::Tensor> key_bias, double scale, int64_t status_ptr,
-                            c10::optional<torch::Tensor> packed);
+                            c10::optional<torch::Tensor> packed, c10::optional<torch::Tensor> trace);
 bool attention_ready();
 // comm.cu
 void register_comm(pybind11::module& m);

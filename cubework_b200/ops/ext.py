@@ -251,4 +251,5 @@ def attention_bwd(dout, qkv, out, lse, causal, key_bias, scale):
     m = require()
     lse, packed = lse
     _count(3 if packed is None else 4)
-    return m.attention_bwd(dout, qkv, out, lse, bool(causal), key_bias, float(scale), m.status_device_ptr(), packed)
+    return m.attention_bwd(dout, qkv, out, lse, bool(causal), key_bias, float(scale), m.status_device_ptr(), packed,
+                           ATTN_TRACE)
