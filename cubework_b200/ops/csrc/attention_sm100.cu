@@ -772,15 +772,35 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
 template <typename T>
 __global__ void attn_pack_kernel(const T* __restrict__ src, T* __restrict__ dst, int B, int Tn, int H, int dh, int parts,
                                  int W) {
-  const int64_t idx = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  // One thread per (b, t, h, part) slice.  A warp's 32 slices are 32 * dh consecutive source elements: they are
+  // fetched with coalesced 16-byte loads into shared memory (when the chunk is 16-byte aligned, i.e. dh even),
+  // and each thread then assembles its zero-padded row from there.
+  extern __shared__ __align__(16) uint8_t pack_smem[];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  T* stage = reinterpret_cast<T*>(pack_smem) + static_cast<size_t>(warp) * 32 * dh;
   const int64_t total = static_cast<int64_t>(B) * Tn * H * parts;
-  if (idx >= total) return;
+  const int64_t first = (static_cast<int64_t>(blockIdx.x) * blockDim.x + warp * 32);
+  if (first >= total) return;
+  const int rows = static_cast<int>(min(static_cast<int64_t>(32), total - first));
+  const T* chunk = src + first * dh;
+  const int n_el = rows * dh;
+  if ((reinterpret_cast<uintptr_t>(chunk) & 15) == 0) {
+    const int n16 = n_el / 8;
+    for (int i = lane; i < n16; i += 32)
+      reinterpret_cast<uint4*>(stage)[i] = reinterpret_cast<const uint4*>(chunk)[i];
+    for (int i = n16 * 8 + lane; i < n_el; i += 32) stage[i] = chunk[i];
+  } else {
+    for (int i = lane; i < n_el; i += 32) stage[i] = chunk[i];
+  }
+  __syncwarp();
+  if (lane >= rows) return;
+  const int64_t idx = first + lane;
   const int part = idx % parts;
   const int64_t bth = idx / parts;
   const int h = bth % H;
   const int64_t bt = bth / H;
   const int t = bt % Tn, b = bt / Tn;
-  const T* s = src + bth * parts * dh + part * dh;
+  const T* s = stage + lane * dh;
   T* d = dst + (((static_cast<int64_t>(part) * B + b) * H + h) * Tn + t) * W;
   for (int c0 = 0; c0 < W; c0 += 8) {
     T tmp[8];
@@ -807,17 +827,41 @@ __global__ void attn_delta_kernel(const T* __restrict__ dout, const T* __restric
 }
 
 // dqkv[b, t, h, 0:dh] = dq_acc[b, h, t, 0:dh]   (fp32 accumulator, padded to DP columns, head-major)
+// One thread per (b, t, h) row: it reads its 4*DP contiguous bytes, converts, and the warp writes the 32 rows one
+// after the other with the lanes along the row (contiguous bytes per store instruction).
 template <typename T>
 __global__ void attn_dq_store_kernel(const float* __restrict__ dq_acc, T* __restrict__ dqkv, int B, int Tn, int H, int dh,
                                      int DP) {
-  const int64_t idx = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
-  if (idx >= static_cast<int64_t>(B) * Tn * H * dh) return;
-  const int d = idx % dh;
-  const int64_t bth = idx / dh;
-  const int h = bth % H;
-  const int64_t bt = bth / H;
-  const int t = bt % Tn, b = bt / Tn;
-  dqkv[bth * 3 * dh + d] = from_f<T>(dq_acc[((static_cast<int64_t>(b) * H + h) * Tn + t) * DP + d]);
+  extern __shared__ __align__(16) uint8_t dq_smem[];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  T* stage = reinterpret_cast<T*>(dq_smem) + static_cast<size_t>(warp) * 32 * DP;
+  const int64_t total = static_cast<int64_t>(B) * Tn * H;
+  const int64_t first = static_cast<int64_t>(blockIdx.x) * blockDim.x + warp * 32;
+  if (first >= total) return;
+  const int rows = static_cast<int>(min(static_cast<int64_t>(32), total - first));
+  if (lane < rows) {
+    const int64_t bth = first + lane;
+    const int h = bth % H;
+    const int64_t bt = bth / H;
+    const int t = bt % Tn, b = bt / Tn;
+    const float4* srow = reinterpret_cast<const float4*>(dq_acc + ((static_cast<int64_t>(b) * H + h) * Tn + t) * DP);
+    for (int q = 0; q < DP / 4; ++q) {
+      const float4 v = srow[q];
+      T* o = stage + lane * DP + q * 4;
+      o[0] = from_f<T>(v.x); o[1] = from_f<T>(v.y); o[2] = from_f<T>(v.z); o[3] = from_f<T>(v.w);
+    }
+  }
+  __syncwarp();
+  T* dst = dqkv + first * 3 * dh;
+  for (int d = lane; d < dh; d += 32)
+    for (int r0 = 0; r0 < rows; r0 += 8) {
+      T v[8];
+#pragma unroll
+      for (int u = 0; u < 8; ++u) v[u] = stage[min(r0 + u, 31) * DP + d];
+#pragma unroll
+      for (int u = 0; u < 8; ++u)
+        if (r0 + u < rows) dst[static_cast<int64_t>(r0 + u) * 3 * dh + d] = v[u];
+    }
 }
 
 // P and dS of one 32-score chunk of a row.  p = exp2(s*sc2 + bias - lse), ds = p * (dp - delta) * scale.
@@ -1289,11 +1333,11 @@ static torch::Tensor pack_heads(const torch::Tensor& src, int B, int T, int H, i
   auto dst = torch::empty({parts, B, H, T, W}, src.options());
   const int64_t total = static_cast<int64_t>(B) * T * H * parts;
   if (src.scalar_type() == torch::kBFloat16) {
-    attn_pack_kernel<__nv_bfloat16><<<(total + 255) / 256, 256, 0, stream>>>(
+    attn_pack_kernel<__nv_bfloat16><<<(total + 127) / 128, 128, 128 * dh * 2, stream>>>(
         reinterpret_cast<const __nv_bfloat16*>(src.data_ptr()), reinterpret_cast<__nv_bfloat16*>(dst.data_ptr()), B, T, H, dh,
         parts, W);
   } else {
-    attn_pack_kernel<__half><<<(total + 255) / 256, 256, 0, stream>>>(reinterpret_cast<const __half*>(src.data_ptr()),
+    attn_pack_kernel<__half><<<(total + 127) / 128, 128, 128 * dh * 2, stream>>>(reinterpret_cast<const __half*>(src.data_ptr()),
                                                                       reinterpret_cast<__half*>(dst.data_ptr()), B, T, H, dh,
                                                                       parts, W);
   }
@@ -1393,12 +1437,11 @@ torch::Tensor attention_bwd(torch::Tensor dout, torch::Tensor qkv, torch::Tensor
   p.dq_acc = dq_acc.data_ptr<float>();
   p.dqkv = dqkv.data_ptr();
   DISPATCH_ATTN(launch_bwd, m, p, stream)
-  const int64_t n = rows * p.dh;
   if (p.is_bf16) {
-    attn_dq_store_kernel<__nv_bfloat16><<<(n + 255) / 256, 256, 0, stream>>>(
+    attn_dq_store_kernel<__nv_bfloat16><<<(rows + 127) / 128, 128, 128 * DPh * 2, stream>>>(
         dq_acc.data_ptr<float>(), reinterpret_cast<__nv_bfloat16*>(dqkv.data_ptr()), p.B, p.T, p.H, p.dh, DPh);
   } else {
-    attn_dq_store_kernel<__half><<<(n + 255) / 256, 256, 0, stream>>>(
+    attn_dq_store_kernel<__half><<<(rows + 127) / 128, 128, 128 * DPh * 2, stream>>>(
         dq_acc.data_ptr<float>(), reinterpret_cast<__half*>(dqkv.data_ptr()), p.B, p.T, p.H, p.dh, DPh);
   }
   C10_CUDA_KERNEL_LAUNCH_CHECK();
