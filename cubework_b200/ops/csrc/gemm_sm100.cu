@@ -12,6 +12,8 @@
 // combinations cover forward (X * W^T), data gradient (dY * W) and weight gradient (dY^T * X) without any
 // transposition pass.  The library equivalents replaced are the cuBLAS calls behind F.linear /
 // torch.matmul / addmm in cubework/module/parallel_{1d,2d,3d}.
+#include <cmath>
+
 #include "gemm_sm100.cuh"
 
 namespace cw {
@@ -296,6 +298,17 @@ void gemm_launch(const GemmArgs& g, cudaStream_t stream) {
   if (g.out_f32 && g.allow_split_k && tiles * 2 <= sms && kb_total >= 16) {
     splits = std::min(std::min(sms / tiles, kb_total / 8), 32);
     if (splits < 1) splits = 1;
+  } else if (g.out_f32 && g.allow_split_k && kb_total >= 64) {
+    // A weight gradient has few, very long tiles (K = tokens): 350 tiles on 148 SMs leave the third wave 36 % full.
+    // Splitting K evens the waves out: take the smallest factor (each one costs a pass of fp32 red.add over the
+    // output) whose last wave is at least 93 % full, else the fullest of 1..8.
+    double best = 0.0;
+    for (int sp = 1; sp <= 8 && kb_total / sp >= 32; ++sp) {
+      const double waves = static_cast<double>(tiles) * sp / sms;
+      const double eff = waves / std::ceil(waves);
+      if (eff > best + 1e-9) { best = eff; splits = sp; }
+      if (eff >= 0.93) break;
+    }
   }
   if (g.force_splits > 0) splits = g.force_splits;
   {
