@@ -1098,7 +1098,6 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
     const uint32_t col_dq = kSep ? kColDQ + (it & 1) * 64 : kColDQ;
     if (tid == 0) {
       tc_fence_after();
-      const uint32_t acc = it > 0 ? 1u : 0u;
 #pragma unroll
       for (int k16 = 0; k16 < kBlk / 16; ++k16)   // dQ[q, d] = sum_key dS[q, key] K[key, d]
         tc_mma_f16(tmem + col_dq, kmajor_desc(smem_u32(ds_img), k16), mnmajor_desc(smem_u32(k_img), k16), idesc_dq, k16 > 0);
