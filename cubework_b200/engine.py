@@ -66,7 +66,8 @@ class Trainer:
         """One optimisation step over ``accum_steps`` micro-batches (a dict, or a list of dicts)."""
         if isinstance(batches, dict):
             batches = [batches]
-        self.model.train()
+        if not self.model.training:      # walking every submodule each step costs milliseconds of host time
+            self.model.train()
         total = None
         n = len(batches)
         for i, batch in enumerate(batches):
