@@ -9,7 +9,15 @@
 Config (both arms): 48 layers, hidden 1600, MLP 6400, vocab 50304, sequence 1024, global batch 32, 1D tensor
 parallel over all N GPUs (strong scaling: the global batch is fixed), AdamW, gradient clipping 1.0, dropout 0,
 synthetic token ids, random-init weights N(0, 0.02).  Heads: 64 x 25 (the reference's ``gpt2_xl`` preset; 25
-heads would not divide 8-way tensor parallelism).
+heads would not divide 8-way tensor parallelism).  Activation checkpointing is ON in both arms
+(``ACTIVATION_CHECKPOINTING``): the reference's default is off, but its materialised ``[batch, heads, T, T]``
+attention scores of 48 layers do not fit one GPU at this batch without it, and both arms must run one
+configuration.  This framework's step without checkpointing is timed too and reported under ``extra``.
+
+This arm runs the 1D layers with row-sharded activations between the linear pairs (``sequence_parallel``):
+all-gather -> GEMM and GEMM -> reduce-scatter inside one kernel each over NVLink peer memory; ``fused_per_step``
+and ``nccl_per_step`` in the printed line count, inside the timed region, the fused launches and what still
+went through NCCL (calls and payload bytes per kind).
 
 One step = forward + backward + clip + optimizer step + zero_grad.  `value` is timed on the device with CUDA
 events around exactly K steps whose inputs already sit on the device; `e2e` repeats the K steps through the
@@ -32,6 +40,7 @@ sys.path.insert(0, ROOT)
 MODEL = dict(vocab_size=50304, max_position_embeddings=1024, hidden_size=1600, num_heads=64, intermediate_size=6400,
              depth=48)
 SEQ, GLOBAL_BATCH = 1024, 32
+ACTIVATION_CHECKPOINTING = True   # one value for both arms (see the module docstring)
 BASELINE_PUBLISHED = None   # the reference publishes no number for this (or any) configuration
 
 
@@ -133,11 +142,12 @@ def run_ours(args):
     from cubework_b200.models import gpt2
     from cubework_b200.ops import ext
     from cubework_b200.optim import FusedAdamW
+    from cubework_b200.parallel import collective, symm_impl
     n = args.gpus
     cube.initialize_distributed(argv=["--tp", "1d", "--tp_size", str(n)])
     dev = torch.device("cuda", torch.cuda.current_device())
-    model = gpt2.GPT2(dropout=0.0, embedding_dropout=0.0, attention_dropout=0.0, checkpoint=False, init_std=0.02,
-                      **MODEL).to(dev)
+    model = gpt2.GPT2(dropout=0.0, embedding_dropout=0.0, attention_dropout=0.0, checkpoint=ACTIVATION_CHECKPOINTING,
+                      init_std=0.02, sequence_parallel=True, **MODEL).to(dev)
     opt = FusedAdamW(model.parameters(), lr=1e-4, weight_decay=0.01)
     trainer = Trainer(model, gpt2.GPT2LMLoss(), opt, amp_dtype=torch.bfloat16, clip=1.0)
     host_batches = _synthetic_batches(torch, 4, GLOBAL_BATCH)
@@ -152,8 +162,14 @@ def run_ours(args):
     if sampler:
         sampler.start()
     launches0 = ext.launch_count()
+    fused0 = dict(symm_impl.STATS)
+    nccl0 = collective.stats_snapshot()
     ms = _time_steps(torch, dist, lambda i: trainer.step(dev_batches[i % len(dev_batches)]), args.steps)
     launches = ext.launch_count() - launches0
+    fused = {k: (v - fused0.get(k, 0)) / args.steps for k, v in symm_impl.STATS.items()}
+    nccl = {k: {"calls": (v[0] - nccl0.get(k, (0, 0))[0]) / args.steps,
+                "mbytes": round((v[1] - nccl0.get(k, (0, 0))[1]) / args.steps / 1e6, 3)}
+            for k, v in collective.stats_snapshot().items()}
     clocks = sampler.stop() if sampler else None
     ext.check_status()
 
@@ -165,6 +181,14 @@ def run_ours(args):
         losses.append(trainer.step(host_batches[i % len(host_batches)]).item())
 
     e2e_ms = _time_steps(torch, dist, e2e_step, args.steps)
+    ext.check_status()
+    # the same model without activation checkpointing (this framework does not need it at this size)
+    for blk in model.blocks:
+        blk.checkpoint = False
+    for i in range(2):
+        trainer.step(dev_batches[i % len(dev_batches)])
+    nockpt_ms = _time_steps(torch, dist, lambda i: trainer.step(dev_batches[i % len(dev_batches)]), args.steps)
+    ext.check_status()
     tokens = GLOBAL_BATCH * SEQ * args.steps
     if dist.get_rank() == 0:
         value = tokens / (ms / 1e3)
@@ -175,14 +199,18 @@ def run_ours(args):
             "data": "synthetic token ids (uniform), random-init weights N(0,0.02)", "impl": "ours",
             "config": {"model": "GPT-2 XL-shape (48L, hidden 1600, 64 heads x 25, MLP 6400, vocab 50304)",
                        "global_batch": GLOBAL_BATCH, "seq_len": SEQ, "parallelism": f"tp{n} (1D)",
-                       "optimizer": "AdamW + clip 1.0", "activation_checkpointing": False,
+                       "optimizer": "AdamW + clip 1.0", "activation_checkpointing": ACTIVATION_CHECKPOINTING,
                        "l2": "working set >> L2 (126 MB); no flush between steps"},
             "clocks": clocks,
             "e2e": {"value": tokens / (e2e_ms / 1e3), "unit": "tokens/s", "ms_per_step": e2e_ms / args.steps,
                     "h2d_bytes_per_step": trainer.h2d_bytes // args.steps, "d2h_bytes_per_step": 4,
                     "last_loss": losses[-1]},
             "gpu_launches": launches,
-            "attention_kernel": "own" if ext.has("attention") else "library (interim)",
+            "sequence_parallel": n > 1,
+            "fused_per_step": fused,
+            "nccl_per_step": nccl,
+            "extra": {"activation_checkpointing_off": {"value": tokens / (nockpt_ms / 1e3), "unit": "tokens/s",
+                                                       "ms_per_step": nockpt_ms / args.steps}},
         }
         print(json.dumps(line), flush=True)
     cube.destroy_distributed()
@@ -223,7 +251,8 @@ def run_reference(args):
     sys.argv = [sys.argv[0], "--tp", "1d", "--tp_size", str(n)]
     cubework.initialize_distributed()
     dev = torch.device("cuda", torch.cuda.current_device())
-    model = ref_gpt2.GPT2(dropout=0.0, embedding_dropout=0.0, attention_dropout=0.0, checkpoint=True, **MODEL).to(dev)
+    model = ref_gpt2.GPT2(dropout=0.0, embedding_dropout=0.0, attention_dropout=0.0,
+                          checkpoint=ACTIVATION_CHECKPOINTING, **MODEL).to(dev)
     with torch.no_grad():
         for p in model.parameters():
             if p.dim() >= 2:
@@ -272,7 +301,7 @@ def run_reference(args):
             "data": "synthetic token ids (uniform), random-init weights N(0,0.02)", "impl": "reference",
             "config": {"model": "GPT-2 XL-shape (48L, hidden 1600, 64 heads x 25, MLP 6400, vocab 50304)",
                        "global_batch": GLOBAL_BATCH, "seq_len": SEQ, "parallelism": f"tp{n} (1D)",
-                       "optimizer": "AdamW + clip 1.0", "activation_checkpointing": True,
+                       "optimizer": "AdamW + clip 1.0", "activation_checkpointing": ACTIVATION_CHECKPOINTING,
                        "l2": "working set >> L2 (126 MB); no flush between steps"},
             "clocks": clocks,
             "e2e": {"value": tokens / (e2e_ms / 1e3), "unit": "tokens/s", "ms_per_step": e2e_ms / args.steps,

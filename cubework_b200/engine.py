@@ -12,6 +12,7 @@ import contextlib
 import torch
 
 from .parallel.common import synchronize as _sync_async_grads
+from .parallel.ops_1d import PARTIAL_GRAD, reduce_partial_grads
 from .utils.clip_grad import clip_grad_norm
 
 
@@ -30,6 +31,9 @@ class Trainer:
         self._copy_stream = torch.cuda.Stream() if self.device.type == "cuda" else None
         self.h2d_bytes = 0
         self.steps = 0
+        # replicated parameters applied to row-sharded activations (1D sequence_parallel): summed over the group
+        self._partial_params = [p for p in model.parameters() if getattr(p, PARTIAL_GRAD, False)]
+        self.status_interval = 16     # steps between reads of the kernels' host-mapped error word
 
     @staticmethod
     def _default_forward(model, batch):
@@ -86,6 +90,8 @@ class Trainer:
                     scaled.backward()
             total = loss.detach() if total is None else total + loss.detach()
         _sync_async_grads()
+        if self._partial_params:
+            reduce_partial_grads(self._partial_params)
         if self.scaler is not None:
             self.scaler.unscale_(self.optimizer)
         if self.clip is not None and self.clip > 0:
@@ -99,10 +105,30 @@ class Trainer:
             self.lr_scheduler.step()
         self.optimizer.zero_grad(set_to_none=True)
         self.steps += 1
+        if self.device.type == "cuda" and self.steps % self.status_interval == 0:
+            self.check_device_status()
         return total / n if n > 1 else total
+
+    def check_device_status(self):
+        """Raise if a kernel of this package gave up on a bounded wait (a peer that never arrived, a stage that
+        never landed) since the last check.  Reading the host-mapped word costs no synchronisation, so a failure
+        is reported at the latest ``status_interval`` steps after it happened; a failed fused launch leaves its
+        output incomplete, and the peer-memory workspaces are released so that the next fused call starts from
+        fresh epochs."""
+        from .ops import ext
+        if not ext.loaded():
+            return
+        try:
+            ext.check_status()
+        except RuntimeError:
+            from .parallel import symm
+            symm.invalidate_all()
+            raise
 
     @torch.no_grad()
     def evaluate(self, batch):
+        if self.device.type == "cuda":
+            self.check_device_status()
         self.model.eval()
         batch = self.to_device(batch)
         with self._autocast():

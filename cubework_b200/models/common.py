@@ -20,14 +20,15 @@ class SelfAttention(nn.Module):
     """
 
     def __init__(self, hidden_size, num_heads, attention_dropout=0.0, dropout=0.0, bias=True, causal=False,
-                 qkv_kw=None, out_kw=None, out_bias=True):
+                 qkv_kw=None, out_kw=None, out_bias=True, sequence_parallel=False):
         super().__init__()
         self.head_dim = hidden_size // num_heads
         self.causal = causal
-        self.query_key_value = cube_nn.Linear(hidden_size, 3 * hidden_size, bias=bias, **(qkv_kw or {}))
+        sp = dict(sequence_parallel=sequence_parallel)
+        self.query_key_value = cube_nn.Linear(hidden_size, 3 * hidden_size, bias=bias, **sp, **(qkv_kw or {}))
         self.attention_dropout_p = attention_dropout
-        self.dense = cube_nn.Linear(hidden_size, hidden_size, bias=out_bias, **(out_kw or {}))
-        self.dropout = cube_nn.Dropout(dropout)
+        self.dense = cube_nn.Linear(hidden_size, hidden_size, bias=out_bias, **sp, **(out_kw or {}))
+        self.dropout = cube_nn.Dropout(dropout, **sp)
         if attention_dropout:
             raise NotImplementedError("dropout on attention probabilities is not supported by the fused kernel")
 
@@ -42,12 +43,14 @@ class SelfAttention(nn.Module):
 class MLP(nn.Module):
 
     def __init__(self, hidden_size, intermediate_size, activation="gelu", dropout=0.0, bias=True, kw1=None,
-                 kw2=None, inner_dropout=0.0):
+                 kw2=None, inner_dropout=0.0, sequence_parallel=False):
         super().__init__()
-        self.dense_1 = cube_nn.Linear(hidden_size, intermediate_size, bias=bias, activation=activation, **(kw1 or {}))
+        sp = dict(sequence_parallel=sequence_parallel)
+        self.dense_1 = cube_nn.Linear(hidden_size, intermediate_size, bias=bias, activation=activation, **sp,
+                                      **(kw1 or {}))
         self.inner_dropout = cube_nn.Dropout(inner_dropout)
-        self.dense_2 = cube_nn.Linear(intermediate_size, hidden_size, bias=bias, **(kw2 or {}))
-        self.dropout = cube_nn.Dropout(dropout)
+        self.dense_2 = cube_nn.Linear(intermediate_size, hidden_size, bias=bias, **sp, **(kw2 or {}))
+        self.dropout = cube_nn.Dropout(dropout, **sp)
 
     def forward(self, x):
         return self.dropout(self.dense_2(self.inner_dropout(self.dense_1(x))))

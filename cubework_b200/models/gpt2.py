@@ -17,34 +17,39 @@ from .common import MLP, SelfAttention, key_bias_from_mask, maybe_checkpoint, no
 class GPT2Embedding(nn.Module):
 
     def __init__(self, embedding_size, vocab_size, max_position_embeddings, padding_idx=None, dropout=0.0,
-                 init_std=None):
+                 init_std=None, sequence_parallel=False):
         super().__init__()
         kw = {} if init_std is None else dict(weight_initializer=normal_init(init_std))
         self.word_embeddings = cube_nn.Embedding(vocab_size, embedding_size, vocab_parallel=True,
-                                                 padding_idx=padding_idx, **kw)
+                                                 padding_idx=padding_idx, sequence_parallel=sequence_parallel, **kw)
         self.position_embeddings = cube_nn.Embedding(max_position_embeddings, embedding_size, **kw)
-        self.dropout = cube_nn.Dropout(dropout)
+        self.sequence_parallel = sequence_parallel
+        self.dropout = cube_nn.Dropout(dropout, sequence_parallel=sequence_parallel)
 
     def forward(self, input_ids):
         t = input_ids.size(1)
         pos = torch.arange(t, dtype=torch.long, device=input_ids.device).unsqueeze(0)
-        return self.dropout(self.word_embeddings(input_ids) + self.position_embeddings(pos))
+        pe = self.position_embeddings(pos)
+        if self.sequence_parallel:    # the [1, T, H] position rows are added to this rank's sequences only
+            pe = cube_nn.sum_grad_over_rows(pe)
+        return self.dropout(self.word_embeddings(input_ids) + pe)
 
 
 class GPT2Block(nn.Module):
 
     def __init__(self, hidden_size, num_heads, intermediate_size, attention_dropout=0.0, dropout=0.0,
                  layernorm_epsilon=1e-5, bias=True, apply_post_layernorm=False, checkpoint=False, init_std=None,
-                 out_std=None):
+                 out_std=None, sequence_parallel=False):
         super().__init__()
         self.checkpoint, self.apply_post_layernorm = checkpoint, apply_post_layernorm
         wi = None if init_std is None else dict(weight_initializer=normal_init(init_std))
         wo = None if out_std is None else dict(weight_initializer=normal_init(out_std))
-        self.norm1 = cube_nn.LayerNorm(hidden_size, eps=layernorm_epsilon)
+        sp = dict(sequence_parallel=sequence_parallel)
+        self.norm1 = cube_nn.LayerNorm(hidden_size, eps=layernorm_epsilon, **sp)
         self.attn = SelfAttention(hidden_size, num_heads, attention_dropout, dropout, bias=bias, causal=True,
-                                  qkv_kw=wi, out_kw=wo)
-        self.norm2 = cube_nn.LayerNorm(hidden_size, eps=layernorm_epsilon)
-        self.mlp = MLP(hidden_size, intermediate_size, "gelu", dropout, bias=bias, kw1=wi, kw2=wo)
+                                  qkv_kw=wi, out_kw=wo, **sp)
+        self.norm2 = cube_nn.LayerNorm(hidden_size, eps=layernorm_epsilon, **sp)
+        self.mlp = MLP(hidden_size, intermediate_size, "gelu", dropout, bias=bias, kw1=wi, kw2=wo, **sp)
 
     def _forward(self, x, key_bias=None):
         h = self.norm1(x)
@@ -76,19 +81,28 @@ class GPT2(nn.Module):
     def __init__(self, vocab_size=50304, max_position_embeddings=1024, hidden_size=768, num_heads=12,
                  intermediate_size=3072, depth=12, dropout=0.1, embedding_dropout=0.1, attention_dropout=0.0,
                  layernorm_epsilon=1e-5, padding_idx=None, bias=True, apply_post_layernorm=False, checkpoint=False,
-                 init_std=None):
+                 init_std=None, sequence_parallel=False):
+        """``sequence_parallel`` (1D tensor parallelism only; ignored elsewhere): hidden states between the
+        attention / MLP pairs hold ``batch / tp`` sequences per rank instead of being replicated; the batch
+        size must be a multiple of the 1D group size."""
         super().__init__()
         out_std = None if init_std is None else init_std
+        sp = dict(sequence_parallel=sequence_parallel)
+        self.sp_size = cube_nn.sequence_parallel_size() if sequence_parallel else 1
         self.embed = GPT2Embedding(hidden_size, vocab_size, max_position_embeddings, padding_idx, embedding_dropout,
-                                   init_std)
+                                   init_std, **sp)
         self.blocks = nn.ModuleList([
             GPT2Block(hidden_size, num_heads, intermediate_size, attention_dropout, dropout, layernorm_epsilon, bias,
-                      apply_post_layernorm, checkpoint, init_std, out_std) for _ in range(depth)
+                      apply_post_layernorm, checkpoint, init_std, out_std, **sp) for _ in range(depth)
         ])
-        self.norm = cube_nn.LayerNorm(hidden_size, eps=layernorm_epsilon)
-        self.head = cube_nn.Classifier(hidden_size, vocab_size, weight=self.embed.word_embeddings.weight, bias=False)
+        self.norm = cube_nn.LayerNorm(hidden_size, eps=layernorm_epsilon, **sp)
+        self.head = cube_nn.Classifier(hidden_size, vocab_size, weight=self.embed.word_embeddings.weight, bias=False,
+                                       **sp)
 
     def forward(self, input_ids, attention_mask=None):
+        if self.sp_size > 1 and input_ids.size(0) % self.sp_size != 0:
+            raise ValueError(f"sequence_parallel needs a batch ({input_ids.size(0)}) divisible by the tensor "
+                             f"parallel size ({self.sp_size})")
         x = self.embed(input_ids)
         key_bias = key_bias_from_mask(attention_mask)
         for block in self.blocks:

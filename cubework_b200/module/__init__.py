@@ -3,7 +3,8 @@ layers, loss, metrics, initializers, plus the per-mode classes under their refer
 from ..parallel import init
 from ..parallel.common import synchronize
 from ..parallel.facade import (Classifier, DropPath, Dropout, Embedding, LayerNorm, Linear, PatchEmbedding,
-                               partition_batch)
+                               gather_rows, mark_partial_grad, partition_batch, scatter_rows,
+                               sequence_parallel_size, sum_grad_over_rows)
 from ..parallel.init import *  # noqa: F401,F403
 from ..parallel.layers_1d import (Classifier1D, Dropout1D, Embedding1D, LayerNorm1D, Linear1D, Linear1D_Col,
                                   Linear1D_Row, PatchEmbedding1D, VocabParallelClassifier1D,

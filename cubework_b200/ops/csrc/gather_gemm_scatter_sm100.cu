@@ -86,6 +86,11 @@ struct GgsParams {
   void* out;                 // local [Ms or M][ldo]
   int ldo;
   const float* bias;         // optional, indexed by output column
+  int act;                   // activation applied by the tile's owner after the bias (kActNone / Gelu / Relu)
+  void* z_out;               // optional copy of the value before the activation, input dtype, same layout as `out`
+  // Row-block order of a product whose A operand is gathered along its rows (and is not scattered): this rank's
+  // own rows first, then panel by panel over the other sources in the order their pushes arrive.
+  int m_remap, m_rps;        // enabled; row blocks per source
   int* status;
 };
 
@@ -110,6 +115,18 @@ struct TileInfo {
 __device__ __forceinline__ TileInfo tile_info(const GgsParams& p, int owner, int li, int kb_total) {
   int tm, tn, kb0, kb1;
   decode_work(li, p.tiles_m * p.tiles_n, p.tiles_m, p.tiles_n, kb_total, 1, tm, tn, kb0, kb1);
+  if (p.m_remap) {
+    // logical position -> row block: [own source's blocks][block 0 of every other source][block 1 ...] ...
+    // source s pushes to this rank in step (me - s - 1) mod n of each of its panel rounds
+    const int n = p.va.n, me = p.va.me;
+    if (tm < p.m_rps) {
+      tm += me * p.m_rps;
+    } else {
+      const int q = tm - p.m_rps;
+      const int pnl = q / (n - 1), si = q - pnl * (n - 1);
+      tm = ((me + n - 1 - si) % n) * p.m_rps + pnl;
+    }
+  }
   TileInfo t;
   t.orow = tm * kBM;
   t.ocol = tn * kFusedBN;
@@ -611,9 +628,19 @@ gather_gemm_scatter_kernel(const __grid_constant__ CUtensorMap tma_a, const __gr
               for (int j = 0; j < 32; ++j)
                 if (c0 + j < ti.cols) v[j] += __ldg(p.bias + ti.ocol + c0 + j);
             }
-            if (r < ti.rows)
-              store_row(out + static_cast<size_t>(ti.orow + r) * p.ldo + ti.ocol + c0, v, vec_ok && c0 + 32 <= ti.cols,
-                        ti.cols - c0);
+            if (r < ti.rows) {
+              const size_t o = static_cast<size_t>(ti.orow + r) * p.ldo + ti.ocol + c0;
+              if (p.z_out != nullptr)
+                store_row<InT>(reinterpret_cast<InT*>(p.z_out) + o, v, (p.ldo % 8 == 0) && c0 + 32 <= ti.cols, ti.cols - c0);
+              if (p.act == kActGelu) {
+#pragma unroll
+                for (int j = 0; j < 32; ++j) v[j] = gelu_f(v[j]);
+              } else if (p.act == kActRelu) {
+#pragma unroll
+                for (int j = 0; j < 32; ++j) v[j] = fmaxf(v[j], 0.f);
+              }
+              store_row(out + o, v, vec_ok && c0 + 32 <= ti.cols, ti.cols - c0);
+            }
           } else {
 #pragma unroll
             for (int q = 0; q < 4; ++q) {
@@ -725,7 +752,7 @@ static void gather_gemm_scatter(torch::Tensor a, torch::Tensor b, bool trans_a, 
                                 std::vector<int64_t> ga_bufs, std::vector<int64_t> ga_flags, std::vector<int64_t> gb,
                                 std::vector<int64_t> gb_bufs, std::vector<int64_t> gb_flags, std::vector<int64_t> sc,
                                 std::vector<int64_t> sc_stage, std::vector<int64_t> sc_flags, int64_t num_comm_ctas,
-                                int64_t status_ptr) {
+                                int64_t status_ptr, int64_t act, c10::optional<torch::Tensor> z_out) {
   TORCH_CHECK(a.is_cuda() && b.is_cuda() && a.dim() == 2 && b.dim() == 2 && a.is_contiguous() && b.is_contiguous());
   TORCH_CHECK(a.scalar_type() == b.scalar_type() && out.is_contiguous() && out.dim() == 2);
   TORCH_CHECK(a.scalar_type() == torch::kBFloat16 || a.scalar_type() == torch::kFloat16);
@@ -797,6 +824,19 @@ static void gather_gemm_scatter(torch::Tensor a, torch::Tensor b, bool trans_a, 
     p.bias = bias_f.data_ptr<float>();
   }
   p.status = reinterpret_cast<int*>(status_ptr);
+  p.act = static_cast<int>(act);
+  p.z_out = nullptr;
+  if (z_out.has_value() && z_out->defined()) {
+    TORCH_CHECK(z_out->scalar_type() == a.scalar_type() && z_out->is_contiguous() && z_out->sizes() == out.sizes(),
+                "pre-activation output must match the output's shape and the operands' dtype");
+    p.z_out = z_out->data_ptr();
+  }
+  p.m_remap = 0; p.m_rps = 0;
+  if (p.va.live && p.va.g == 0 && ak && p.sc_dim < 0 && p.va.own_direct && p.va.panel_rows == kBM &&
+      p.va.R % kBM == 0) {
+    p.m_remap = 1;
+    p.m_rps = p.va.R / kBM;
+  }
   // start the K loop at the local shard when K is the gathered dimension
   const int kb_total = (K + kBK - 1) / kBK;
   p.k_start = 0;

@@ -7,9 +7,11 @@ when ``async_op`` is set.
 
 Differences: communication accounting is built in (each call reports its algorithm bytes and a pair
 of stream events to the active :class:`~cubework_b200.utils.profiling.CommProfiler`, so profiling
-needs neither monkey-patching nor a host synchronisation per call), and CUDA tensors that fit the
-symmetric-memory workspace go through this package's own peer-memory kernels
-(:mod:`cubework_b200.parallel.symm`) instead of NCCL.
+needs neither monkey-patching nor a host synchronisation per call).  Every function here is a
+``torch.distributed`` (NCCL / gloo) call; the collectives that follow or precede a GEMM do not come
+through this module on CUDA but run inside the GEMM kernel (:mod:`cubework_b200.parallel.fused`).
+``STATS`` counts calls and payload bytes per kind, so a caller can verify what still goes through
+the library on a hot path.
 """
 from typing import Optional
 
@@ -20,6 +22,17 @@ from torch.distributed import ReduceOp
 from .mesh import ParallelMode
 
 _profiler = None  # set by CommProfiler.start()
+STATS = {}        # kind -> [calls, payload bytes] issued by this process through the wrappers below
+
+
+def _tally(kind, tensor):
+    rec = STATS.setdefault(kind, [0, 0])
+    rec[0] += 1
+    rec[1] += tensor.numel() * tensor.element_size()
+
+
+def stats_snapshot():
+    return {k: tuple(v) for k, v in STATS.items()}
 
 
 def _set_profiler(p):
@@ -75,6 +88,7 @@ def all_gather(tensor: torch.Tensor, dim: int, parallel_mode: ParallelMode, asyn
     dim = dim % tensor.dim()
     src = tensor.contiguous() if dim == 0 else tensor.transpose(0, dim).contiguous()
     out = src.new_empty((n * src.shape[0], ) + tuple(src.shape[1:]))
+    _tally("all_gather", out)
     ticket = _Ticket("all_gather", _nbytes(out) * (n - 1) // n, tensor)
     work = dist.all_gather_into_tensor(out, src, group=parallel_mode.group_for(tensor), async_op=async_op)
     if dim != 0:
@@ -94,6 +108,7 @@ def reduce_scatter(tensor: torch.Tensor,
     assert tensor.shape[dim] % n == 0, f"dim {dim} of {tuple(tensor.shape)} is not divisible by {n}"
     src = tensor.contiguous() if dim == 0 else tensor.transpose(0, dim).contiguous()
     out = src.new_empty((src.shape[0] // n, ) + tuple(src.shape[1:]))
+    _tally("reduce_scatter", src)
     ticket = _Ticket("reduce_scatter", _nbytes(src) * (n - 1) // n, tensor)
     group = parallel_mode.group_for(tensor)
     if tensor.device.type == "cpu":
@@ -117,6 +132,7 @@ def all_reduce(tensor: torch.Tensor,
     if n == 1:
         return (tensor, None) if async_op else tensor
     out = tensor.contiguous()
+    _tally("all_reduce", out)
     ticket = _Ticket("all_reduce", _nbytes(out) * 2 * (n - 1) // n, tensor)
     work = dist.all_reduce(out, op=op, group=parallel_mode.group_for(tensor), async_op=async_op)
     return _finish(out, work, ticket, async_op)
@@ -127,6 +143,7 @@ def broadcast(tensor: torch.Tensor, src: int, parallel_mode: ParallelMode, async
     if parallel_mode.world_size == 1:
         return (tensor, None) if async_op else tensor
     out = tensor.contiguous()
+    _tally("broadcast", out)
     ticket = _Ticket("broadcast", _nbytes(out), tensor)
     work = dist.broadcast(out, src=src, group=parallel_mode.group_for(tensor), async_op=async_op)
     return _finish(out, work, ticket, async_op)
@@ -140,6 +157,7 @@ def reduce(tensor: torch.Tensor,
     if parallel_mode.world_size == 1:
         return (tensor, None) if async_op else tensor
     out = tensor.contiguous()
+    _tally("reduce", out)
     ticket = _Ticket("reduce", _nbytes(out), tensor)
     work = dist.reduce(out, dst=dst, op=op, group=parallel_mode.group_for(tensor), async_op=async_op)
     return _finish(out, work, ticket, async_op)

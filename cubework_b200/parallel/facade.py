@@ -7,6 +7,12 @@ vocab-parallel variant when the last embedding/classifier set ``env.vocab_parall
 
 Extension: ``Linear(..., activation="gelu"|"relu")`` fuses bias + activation into the GEMM epilogue
 (1D column-parallel and unsharded linears); other modes apply the activation after the layer.
+
+Extension: ``sequence_parallel=True`` on ``Linear`` / ``LayerNorm`` / ``Embedding`` / ``Classifier`` /
+``Dropout`` selects, in 1D mode, the layout in which activations between column/row linear pairs are
+sharded along their leading dimension (see :mod:`cubework_b200.parallel.layers_1d`).  The other modes
+shard their activations already and ignore the flag.  :func:`sequence_parallel_size` tells a model by how
+much the leading dimension shrinks.
 """
 import math
 from typing import Callable
@@ -58,7 +64,47 @@ _parallel_patchembedding = {None: PatchEmbeddingSTD, "1d": _patch_embedding_1d, 
 _parallel_split_batch = {"2d": split_batch_2d, "3d": split_batch_3d}
 
 __all__ = ["Linear", "LayerNorm", "Embedding", "Classifier", "PatchEmbedding", "Dropout", "DropPath",
-           "partition_batch"]
+           "partition_batch", "sequence_parallel_size", "scatter_rows", "gather_rows", "mark_partial_grad",
+           "sum_grad_over_rows"]
+
+
+def sequence_parallel_size():
+    """Number of row shards that ``sequence_parallel=True`` layers use: the 1D group size, else 1."""
+    if get_tensor_parallel_mode() == "1d" and pm.PARALLEL_1D.is_initialized():
+        return pm.PARALLEL_1D.world_size
+    return 1
+
+
+def scatter_rows(x):
+    """This rank's block of the leading dimension of a replicated tensor (identity outside 1D mode)."""
+    from .ops_1d import scatter_rows as _s
+    return _s(x, pm.PARALLEL_1D) if sequence_parallel_size() > 1 else x
+
+
+def gather_rows(x):
+    """Inverse of :func:`scatter_rows`."""
+    from .ops_1d import gather_rows as _g
+    return _g(x, pm.PARALLEL_1D) if sequence_parallel_size() > 1 else x
+
+
+def sum_grad_over_rows(x):
+    """Identity; in backward the gradient is summed over the 1D group.  For a replicated tensor (a position
+    table's rows, a broadcast bias) that is consumed by row-sharded computation and produced by sharded
+    parameters, where completing the parameter gradient afterwards would mix different shards."""
+    from .ops_1d import reduce_grad
+    return reduce_grad(x, pm.PARALLEL_1D) if sequence_parallel_size() > 1 else x
+
+
+def mark_partial_grad(param):
+    """Declare that ``param`` is replicated but applied to row-sharded activations (1D ``sequence_parallel``), so
+    its gradient must be summed over the group after the backward pass (the ``Trainer`` does it)."""
+    from .ops_1d import mark_partial_grad as _m
+    if sequence_parallel_size() > 1:
+        _m(param)
+
+
+def _sp_kwargs(mode, sequence_parallel):
+    return dict(sequence_parallel=True) if (sequence_parallel and mode == "1d") else {}
 
 
 def partition_batch(input_):
@@ -115,11 +161,11 @@ def _to(module, dtype):
 
 class LayerNorm(nn.Module):
 
-    def __init__(self, normalized_shape: int, eps=1e-05, dtype=None):
+    def __init__(self, normalized_shape: int, eps=1e-05, dtype=None, sequence_parallel=False):
         super().__init__()
         mode = get_tensor_parallel_mode()
         norm = _PlainLayerNorm(normalized_shape, eps) if mode is None else \
-            _parallel_layernorm[mode](normalized_shape, eps=eps)
+            _parallel_layernorm[mode](normalized_shape, eps=eps, **_sp_kwargs(mode, sequence_parallel))
         self.norm = _to(norm, dtype)
 
     def forward(self, *args, **kwargs):
@@ -133,9 +179,10 @@ class Linear(nn.Module):
 
     def __init__(self, in_features: int, out_features: int, bias: bool = True, dtype=None,
                  weight_initializer: Callable = _W_INIT, bias_initializer: Callable = _B_INIT, activation=None,
-                 **kwargs):
+                 sequence_parallel=False, **kwargs):
         super().__init__()
         mode = get_tensor_parallel_mode()
+        kwargs.update(_sp_kwargs(mode, sequence_parallel))
         self._post_act = None
         if mode is None:
             lin = _PlainLinear(in_features, out_features, bias, activation)
@@ -167,12 +214,16 @@ class Linear(nn.Module):
 class Classifier(nn.Module):
 
     def __init__(self, in_features: int, num_classes: int, weight: nn.Parameter = None, bias: bool = True,
-                 dtype=None, weight_initializer: Callable = _W_INIT, bias_initializer: Callable = _B_INIT):
+                 dtype=None, weight_initializer: Callable = _W_INIT, bias_initializer: Callable = _B_INIT,
+                 sequence_parallel=False):
         super().__init__()
         mode = get_tensor_parallel_mode()
-        table = _vocab_parallel_classifier if (env.vocab_parallel and mode is not None) else _parallel_classifier
+        vocab_parallel = env.vocab_parallel and mode is not None
+        table = _vocab_parallel_classifier if vocab_parallel else _parallel_classifier
+        if sequence_parallel and mode == "1d" and not vocab_parallel:
+            raise ValueError("sequence_parallel needs the vocab-parallel classifier in 1D mode")
         lin = table[mode](in_features, num_classes, weight=weight, bias=bias, weight_initializer=weight_initializer,
-                          bias_initializer=bias_initializer)
+                          bias_initializer=bias_initializer, **_sp_kwargs(mode, sequence_parallel))
         self.linear = _to(lin, dtype)
 
     def forward(self, *args, **kwargs):
@@ -185,10 +236,12 @@ class Classifier(nn.Module):
 class Embedding(nn.Module):
 
     def __init__(self, num_embeddings: int, embedding_dim: int, vocab_parallel: bool = False,
-                 padding_idx: int = None, dtype=None, weight_initializer: Callable = init.normal_(), *args,
-                 **kwargs):
+                 padding_idx: int = None, dtype=None, weight_initializer: Callable = init.normal_(),
+                 sequence_parallel=False, *args, **kwargs):
         super().__init__()
         mode = get_tensor_parallel_mode()
+        if vocab_parallel:
+            kwargs.update(_sp_kwargs(mode, sequence_parallel))
         if mode is None:
             emb = _PlainEmbedding(num_embeddings, embedding_dim, padding_idx)
             weight_initializer(emb.weight, fan_in=num_embeddings, fan_out=embedding_dim)
@@ -229,11 +282,12 @@ class PatchEmbedding(nn.Module):
 
 class Dropout(nn.Module):
 
-    def __init__(self, p: float = 0.5, inplace: bool = False):
+    def __init__(self, p: float = 0.5, inplace: bool = False, sequence_parallel=False):
         super().__init__()
         self.tensor_parallel = get_tensor_parallel_mode()
         self.p = p
-        self.drop = Dropout1D(p, inplace) if self.tensor_parallel == "1d" else nn.Dropout(p, inplace)
+        self.drop = Dropout1D(p, inplace, **_sp_kwargs("1d", sequence_parallel)) if self.tensor_parallel == "1d" \
+            else nn.Dropout(p, inplace)
 
     def forward(self, x):
         if self.p == 0.0 or not self.training:

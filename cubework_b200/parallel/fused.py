@@ -34,34 +34,51 @@ def _live(spec):
 def gather_gemm_reduce(a: torch.Tensor, b: torch.Tensor, trans_a: bool = False, trans_b: bool = False, *,
                        gather_a: Spec = None, gather_b: Spec = None, scatter: Spec = None,
                        reduce: Optional[ParallelMode] = None, bias: Optional[torch.Tensor] = None,
-                       out_dtype: Optional[torch.dtype] = None, keep_gathered: bool = False):
-    """``C = reduce( op(gather(a)) @ op(gather(b)) ) + bias``.
+                       out_dtype: Optional[torch.dtype] = None, keep_gathered=False, act: Optional[str] = None,
+                       pre_act_out: bool = False):
+    """``C = act( reduce( op(gather(a)) @ op(gather(b)) ) + bias )``.
 
     ``gather_a/gather_b = (mode, dim)`` all-gather the stored operand along ``dim`` over ``mode``;
     ``scatter = (mode, dim)`` reduce-scatters the product along ``dim``; ``reduce = mode`` all-reduces
-    it instead.  ``bias`` is added after the reduction.  With ``keep_gathered`` the gathered operands
-    are returned too (the backward of the 3D linear reuses them): ``(C, a_full, b_full)``.
+    it instead.  ``bias`` is added after the reduction, then the activation (``"gelu"`` / ``"relu"``).
+    Returns ``C``, followed by the value before the activation when ``pre_act_out`` is set, followed by
+    the gathered operands ``a_full, b_full`` when ``keep_gathered`` is set (the backward of the 3D and
+    of the row-sharded 1D linears reuses them).  ``keep_gathered="view"`` allows the gathered operands
+    to be views of the communication workspace that are only valid until the next fused call on the
+    same group: for consumers that run next on the same stream.
     """
     assert not (scatter is not None and reduce is not None)
     out_dtype = out_dtype or a.dtype
     if ops.use_kernels(a) and symm.available():
         res = symm.fused_gather_gemm_reduce(a, b, trans_a, trans_b, gather_a, gather_b, scatter, reduce, bias,
-                                            out_dtype, keep_gathered)
+                                            out_dtype, keep_gathered, act, pre_act_out)
         if res is not None:
             return res
     a_full = all_gather(a, gather_a[1], gather_a[0]).contiguous() if _live(gather_a) else a
     b_full = all_gather(b, gather_b[1], gather_b[0]).contiguous() if _live(gather_b) else b
     needs_comm = _live(scatter) or (reduce is not None and reduce.world_size > 1)
-    c = ops.gemm(a_full, b_full, trans_a, trans_b, bias=None if needs_comm else bias, out_dtype=out_dtype)
-    if _live(scatter):
-        c = reduce_scatter(c, scatter[1], scatter[0]).contiguous()
-    elif reduce is not None and reduce.world_size > 1:
-        c = all_reduce(c, reduce)
-    if needs_comm and bias is not None:
-        c = c + bias.to(c.dtype)
+    z = None
+    if not needs_comm:
+        c = ops.gemm(a_full, b_full, trans_a, trans_b, bias=bias, act=act, out_dtype=out_dtype,
+                     pre_act_out=pre_act_out)
+        if pre_act_out:
+            c, z = c
+    else:
+        c = ops.gemm(a_full, b_full, trans_a, trans_b, out_dtype=out_dtype)
+        if _live(scatter):
+            c = reduce_scatter(c, scatter[1], scatter[0]).contiguous()
+        else:
+            c = all_reduce(c, reduce)
+        if bias is not None:
+            c = c + bias.to(c.dtype)
+        if pre_act_out:
+            z = c
+        if act is not None:
+            c = ops._act(c, act)
+    res = (c, z) if pre_act_out else (c, )
     if keep_gathered:
-        return c, a_full, b_full
-    return c
+        res = res + (a_full, b_full)
+    return res if len(res) > 1 else res[0]
 
 
 def gemm_all_reduce(a, b, trans_a, trans_b, mode, bias=None, out_dtype=None):

@@ -10,6 +10,12 @@ all-gather), ``VocabParallelEmbedding1D`` (W ``[V/n, H]``, masked lookup + all-r
 
 The forward passes call :func:`~cubework_b200.parallel.ops_1d.linear_1d`, so GEMM and all-reduce
 are one kernel on CUDA.  ``activation=`` fuses bias + GELU/ReLU into the column GEMM's epilogue.
+
+Extension (no counterpart in the reference): ``sequence_parallel=True`` keeps the activations *between*
+column/row pairs sharded along their leading dimension (rows of tokens) instead of replicated.  A column
+linear then starts with an all-gather of rows and a row linear ends with a reduce-scatter of rows - the same
+bytes on the wire as the all-reduce they replace - and layer norm, residual adds and dropout in between
+touch ``1/n`` of the rows.  The default (``False``) keeps the reference's replicated semantics.
 """
 import math
 from typing import Callable
@@ -26,8 +32,9 @@ from .collective import broadcast
 from .common import set_tensor_parallel_attribute_by_partition as _stamp
 from .functional import layer_norm, masked_embedding
 from .mesh import pm
-from .ops_1d import (gather_forward_split_backward, get_parallel_input, linear_1d, reduce_input,
-                     set_parallel_input, split_forward_gather_backward)
+from .ops_1d import (gather_forward_split_backward, get_parallel_input, linear_1d, linear_1d_rows,
+                     mark_partial_grad, reduce_input, reduce_scatter_rows, set_parallel_input,
+                     split_forward_gather_backward)
 from .std import PatchEmbeddingSTD
 
 _W_INIT = init.kaiming_uniform_(a=math.sqrt(5))
@@ -44,12 +51,14 @@ class Linear1D_Col(nn.Module):
     """``Y_local = X W_local^T + b_local``; input replicated, output sharded on the last dim."""
 
     def __init__(self, in_features, out_features, bias=True, gather_output=False, skip_bias_add=False,
-                 weight_initializer: Callable = _W_INIT, bias_initializer: Callable = _B_INIT, activation=None):
+                 weight_initializer: Callable = _W_INIT, bias_initializer: Callable = _B_INIT, activation=None,
+                 sequence_parallel=False):
         super().__init__()
         if skip_bias_add and not bias:
             raise ValueError("cannot skip bias addition if bias is None")
         self.in_features, self.out_features = in_features, out_features
         self.gather_output, self.skip_bias_add, self.activation = gather_output, skip_bias_add, activation
+        self.sequence_parallel = sequence_parallel
         n = pm.PARALLEL_1D.world_size
         self.out_features_per_partition = _div(out_features, n, "out_features")
         self.weight = Parameter(torch.empty(self.out_features_per_partition, in_features))
@@ -65,7 +74,10 @@ class Linear1D_Col(nn.Module):
 
     def forward(self, x):
         b = None if self.skip_bias_add else self.bias
-        y = linear_1d(x, self.weight, b, pm.PARALLEL_1D, reduce_bwd=True, act=self.activation)
+        if self.sequence_parallel:      # x holds this rank's rows; the output has all rows
+            y = linear_1d_rows(x, self.weight, b, pm.PARALLEL_1D, "gather", act=self.activation)
+        else:
+            y = linear_1d(x, self.weight, b, pm.PARALLEL_1D, reduce_bwd=True, act=self.activation)
         if self.gather_output:
             y = gather_forward_split_backward(y, pm.PARALLEL_1D, dim=-1)
         return (y, self.bias) if self.skip_bias_add else y
@@ -75,12 +87,14 @@ class Linear1D_Row(nn.Module):
     """``Y = sum_ranks(X_local W_local^T) + b``; input sharded on the last dim, output replicated."""
 
     def __init__(self, in_features, out_features, bias=True, parallel_input=True, skip_bias_add=False,
-                 weight_initializer: Callable = _W_INIT, bias_initializer: Callable = _B_INIT):
+                 weight_initializer: Callable = _W_INIT, bias_initializer: Callable = _B_INIT,
+                 sequence_parallel=False):
         super().__init__()
         if skip_bias_add and not bias:
             raise ValueError("cannot skip bias addition if bias is None")
         self.in_features, self.out_features = in_features, out_features
         self.parallel_input, self.skip_bias_add = parallel_input, skip_bias_add
+        self.sequence_parallel = sequence_parallel
         n = pm.PARALLEL_1D.world_size
         self.input_size_per_partition = _div(in_features, n, "in_features")
         self.weight = Parameter(torch.empty(out_features, self.input_size_per_partition))
@@ -92,6 +106,8 @@ class Linear1D_Row(nn.Module):
         if bias:
             with torch.no_grad():
                 broadcast(self.bias.data, pm.PARALLEL_1D.rank_by_idx(0), pm.PARALLEL_1D)
+            if sequence_parallel:       # added to this rank's rows only
+                mark_partial_grad(self.bias)
         _stamp(self.weight, n, [(-1, "PARALLEL_1D")])
         set_parallel_input(False)
 
@@ -99,26 +115,31 @@ class Linear1D_Row(nn.Module):
         if not self.parallel_input:
             x = split_forward_gather_backward(x, pm.PARALLEL_1D, dim=-1)
         b = None if self.skip_bias_add else self.bias
-        y = linear_1d(x, self.weight, b, pm.PARALLEL_1D, reduce_fwd=True)
+        if self.sequence_parallel:      # the output keeps this rank's rows of the sum
+            y = linear_1d_rows(x, self.weight, b, pm.PARALLEL_1D, "scatter")
+        else:
+            y = linear_1d(x, self.weight, b, pm.PARALLEL_1D, reduce_fwd=True)
         return (y, self.bias) if self.skip_bias_add else y
 
 
 class Linear1D(nn.Module):
 
     def __init__(self, in_features, out_features, bias=True, gather_output=False, skip_bias_add=False,
-                 weight_initializer: Callable = _W_INIT, bias_initializer: Callable = _B_INIT, activation=None):
+                 weight_initializer: Callable = _W_INIT, bias_initializer: Callable = _B_INIT, activation=None,
+                 sequence_parallel=False):
         super().__init__()
         parallel_input = get_parallel_input()
         if not parallel_input:
             self.linear = Linear1D_Col(in_features, out_features, bias=bias, gather_output=gather_output,
                                        skip_bias_add=skip_bias_add, weight_initializer=weight_initializer,
-                                       bias_initializer=bias_initializer, activation=activation)
+                                       bias_initializer=bias_initializer, activation=activation,
+                                       sequence_parallel=sequence_parallel)
         else:
             if activation is not None:
                 raise ValueError("a fused activation needs a column-parallel (replicated-input) linear")
             self.linear = Linear1D_Row(in_features, out_features, bias=bias, parallel_input=parallel_input,
                                        skip_bias_add=skip_bias_add, weight_initializer=weight_initializer,
-                                       bias_initializer=bias_initializer)
+                                       bias_initializer=bias_initializer, sequence_parallel=sequence_parallel)
 
     def forward(self, *args, **kwargs):
         return self.linear(*args, **kwargs)
@@ -128,13 +149,17 @@ class Linear1D(nn.Module):
 
 
 class LayerNorm1D(nn.Module):
-    """Replicated layer norm (activations between 1D blocks are replicated)."""
+    """Replicated layer norm (activations between 1D blocks are replicated).  With ``sequence_parallel`` it is
+    applied to this rank's rows only and its parameter gradients are completed over the group afterwards."""
 
-    def __init__(self, normalized_shape: int, eps=1e-05):
+    def __init__(self, normalized_shape: int, eps=1e-05, sequence_parallel=False):
         super().__init__()
         self.normalized_shape, self.eps = normalized_shape, eps
         self.weight = Parameter(torch.ones(normalized_shape))
         self.bias = Parameter(torch.zeros(normalized_shape))
+        if sequence_parallel:
+            mark_partial_grad(self.weight)
+            mark_partial_grad(self.bias)
 
     def forward(self, x):
         return layer_norm(x, self.weight, self.bias, self.eps)
@@ -177,10 +202,12 @@ class VocabParallelClassifier1D(nn.Module):
     """``logits_local = X W_local^T + b_local`` with W ``[C/n, in]``; output sharded over classes."""
 
     def __init__(self, in_features, num_classes, weight: Parameter = None, bias=True,
-                 weight_initializer: Callable = _W_INIT, bias_initializer: Callable = _B_INIT):
+                 weight_initializer: Callable = _W_INIT, bias_initializer: Callable = _B_INIT,
+                 sequence_parallel=False):
         super().__init__()
         self.in_features, self.num_classes = in_features, num_classes
         self.parallel_input = get_parallel_input()
+        self.sequence_parallel = sequence_parallel
         n = pm.PARALLEL_1D.world_size
         self.num_classes_per_partition = _div(num_classes, n, "num_classes")
         self.has_weight = weight is None
@@ -200,6 +227,8 @@ class VocabParallelClassifier1D(nn.Module):
         env.vocab_parallel = True
 
     def forward(self, x):
+        if self.sequence_parallel:      # x holds this rank's rows; the logits cover all rows, local classes
+            return linear_1d_rows(x, self.weight, self.bias, pm.PARALLEL_1D, "gather")
         return linear_1d(x, self.weight, self.bias, pm.PARALLEL_1D, reduce_bwd=True)
 
 
@@ -229,9 +258,10 @@ class VocabParallelEmbedding1D(nn.Module):
     """Vocabulary-sharded table W ``[V/n, H]``; foreign ids give zeros, then an all-reduce."""
 
     def __init__(self, num_embeddings, embedding_dim, padding_idx=None,
-                 weight_initializer: Callable = init.normal_(), *args, **kwargs):
+                 weight_initializer: Callable = init.normal_(), sequence_parallel=False, *args, **kwargs):
         super().__init__()
         self.num_embeddings, self.embed_dim, self.padding_idx = num_embeddings, embedding_dim, padding_idx
+        self.sequence_parallel = sequence_parallel
         n, r = pm.PARALLEL_1D.world_size, pm.PARALLEL_1D.local_rank
         self.num_embeddings_per_partition = _div(num_embeddings, n, "num_embeddings")
         self.vocab_start_index = r * self.num_embeddings_per_partition
@@ -248,6 +278,8 @@ class VocabParallelEmbedding1D(nn.Module):
 
     def forward(self, ids):
         out = masked_embedding(ids, self.weight, self.vocab_start_index)
+        if self.sequence_parallel:      # every rank looks all ids up; each keeps its rows of the sum
+            return reduce_scatter_rows(out, pm.PARALLEL_1D)
         return reduce_input(out, pm.PARALLEL_1D)
 
 
@@ -255,9 +287,9 @@ class Dropout1D(nn.Module):
     """Dropout that draws from the per-rank TENSOR stream when its input is sharded, and from the
     shared default stream when it is replicated (parallel_1d/module.py:458-472)."""
 
-    def __init__(self, p: float = 0.5, inplace: bool = False):
+    def __init__(self, p: float = 0.5, inplace: bool = False, sequence_parallel=False):
         super().__init__()
-        self.parallel_input = get_parallel_input()
+        self.parallel_input = get_parallel_input() or sequence_parallel   # row shards differ per rank too
         self.p, self.inplace = p, inplace
 
     def forward(self, x):

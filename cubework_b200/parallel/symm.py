@@ -65,9 +65,17 @@ def release_all():
     _WORKSPACES.clear()
 
 
+def invalidate_all():
+    """Forget every workspace without touching the device (after a reported device-side timeout the epochs of
+    the ranks may disagree).  The regions are re-created, with fresh flags, at the next fused call - which is
+    collective, so every rank of a group has to get here (each one's status check fails the same way, or the job
+    is torn down).  The old allocations are released at process exit."""
+    _WORKSPACES.clear()
+
+
 def fused_gather_gemm_reduce(a, b, trans_a, trans_b, gather_a, gather_b, scatter, reduce, bias, out_dtype,
-                             keep_gathered):
+                             keep_gathered, act=None, pre_act_out=False):
     """Returns None when the pattern/shape is not covered, so the caller composes it from parts."""
     from . import symm_impl
     return symm_impl.dispatch(a, b, trans_a, trans_b, gather_a, gather_b, scatter, reduce, bias, out_dtype,
-                              keep_gathered)
+                              keep_gathered, act, pre_act_out)

@@ -161,8 +161,16 @@ def _aligned(t):
     return t if t.data_ptr() % 16 == 0 else t.clone()
 
 
-def fused_gather_gemm_scatter(a, b, trans_a, trans_b, gather_a, gather_b, scatter, bias, out_dtype, keep_gathered):
-    """One launch of ``ops/csrc/gather_gemm_scatter_sm100.cu``; None when the shapes are outside what it covers."""
+_ACT_CODE = {None: 0, "gelu": 1, "relu": 2}
+
+
+def fused_gather_gemm_scatter(a, b, trans_a, trans_b, gather_a, gather_b, scatter, bias, out_dtype, keep_gathered,
+                              act=None, pre_act_out=False):
+    """One launch of ``ops/csrc/gather_gemm_scatter_sm100.cu``; None when the shapes are outside what it covers.
+
+    ``keep_gathered``: False, True (the gathered operands are returned as tensors of their own) or ``"view"``
+    (returned as views of the workspace, valid until the next fused call on the same group: for a consumer that
+    runs next on the same stream).  With ``pre_act_out`` the value before ``act`` is returned after the output."""
     if a.dtype != b.dtype or a.dtype not in _LOWP or out_dtype not in (a.dtype, torch.float32):
         return None
     if a.dim() != 2 or b.dim() != 2 or a.shape[1] % 8 != 0 or b.shape[1] % 8 != 0:
@@ -232,10 +240,11 @@ def fused_gather_gemm_scatter(a, b, trans_a, trans_b, gather_a, gather_b, scatte
         sc_stage = [p + half for p in stage]
         sc_cfg = [sc[1], sc[2], ws.me, ws.epoch]
     out = torch.empty((Ms, Ns), dtype=out_dtype, device=a.device)
+    z = torch.empty((Ms, Ns), dtype=a.dtype, device=a.device) if pre_act_out else None
     ext._count(1)
     STATS["gather_gemm_scatter"] += 1
     m.gather_gemm_scatter(a, b, bool(trans_a), bool(trans_b), bias, out, ga_cfg, ga_bufs, ga_flags, gb_cfg, gb_bufs,
-                          gb_flags, sc_cfg, sc_stage, sc_flags, _PUSH_CTAS, m.status_device_ptr())
+                          gb_flags, sc_cfg, sc_stage, sc_flags, _PUSH_CTAS, m.status_device_ptr(), _ACT_CODE[act], z)
     from . import collective
     if collective._profiler is not None:
         moved = 0
@@ -245,30 +254,36 @@ def fused_gather_gemm_scatter(a, b, trans_a, trans_b, gather_a, gather_b, scatte
         if sc is not None:
             moved += (sc[2] - 1) * Ms * Ns * a.element_size()
         collective._profiler.account("fused_gather_gemm_scatter", moved)
+    res = (out, ) if not pre_act_out else (out, z)
     if not keep_gathered:
-        return out
+        return res if pre_act_out else out
 
     def gathered(plan, cfg, bufs, t):
         if plan is None:
             return t
         n, g = plan[0], plan[1]
         R, C = t.shape
-        # the buffer holds the other ranks' shards (the own one only in some layouts): copy out, then place the own
-        full = m.as_tensor(bufs[cfg[1]], [n, R, C], t.dtype, t.device.index).clone()
-        full[cfg[1]] = t
+        # the buffer holds the other ranks' shards (the own one only in some layouts): place the own one too
+        full = m.as_tensor(bufs[cfg[1]], [n, R, C], t.dtype, t.device.index)
+        if keep_gathered != "view":
+            full = full.clone()
+        full[cfg[1]].copy_(t)
         return full.reshape(n * R, C) if g == 0 else full.permute(1, 0, 2).reshape(R, n * C)
 
-    return out, gathered(ga, ga_cfg, ga_bufs, a), gathered(gb, gb_cfg, gb_bufs, b)
+    return res + (gathered(ga, ga_cfg, ga_bufs, a), gathered(gb, gb_cfg, gb_bufs, b))
 
 
-def dispatch(a, b, trans_a, trans_b, gather_a, gather_b, scatter, reduce, bias, out_dtype, keep_gathered):
+def dispatch(a, b, trans_a, trans_b, gather_a, gather_b, scatter, reduce, bias, out_dtype, keep_gathered, act=None,
+             pre_act_out=False):
     live = lambda s: s is not None and s[0].world_size > 1
     if reduce is not None and reduce.world_size > 1 and not live(gather_a) and not live(gather_b) and not live(scatter):
+        if act is not None or pre_act_out:
+            return None
         out = fused_gemm_all_reduce(a, b, trans_a, trans_b, reduce, bias, out_dtype or a.dtype)
         if out is None:
             return None
         return (out, a, b) if keep_gathered else out
     if (reduce is None or reduce.world_size == 1) and (live(gather_a) or live(gather_b) or live(scatter)):
         return fused_gather_gemm_scatter(a, b, trans_a, trans_b, gather_a, gather_b, scatter, bias,
-                                         out_dtype or a.dtype, keep_gathered)
+                                         out_dtype or a.dtype, keep_gathered, act, pre_act_out)
     return None

@@ -159,6 +159,60 @@ def _check_layers_bf16():
     assert _rel(row.bias.grad, b2r.grad) < 2e-2 and _rel(col.bias.grad, b1r.grad.chunk(n, 0)[r]) < 2e-2
 
 
+def _check_sp_layers_bf16():
+    """Column linear (bias + GELU) -> row linear pair with row-sharded activations on both sides: the all-gather
+    runs inside the first GEMM kernel and the reduce-scatter inside the second (and mirrored in backward); checked
+    against the unsharded fp32 formulation.  Three rounds reuse the workspace halves and epochs."""
+    import torch.distributed as dist
+    import torch.nn.functional as F
+
+    import cubework_b200.module as nn_
+    from cubework_b200.distributed import ParallelManager as pm
+    from cubework_b200.ops import ext
+    from cubework_b200.parallel import symm, symm_impl
+    from cubework_b200.parallel.ops_1d import reduce_partial_grads, set_parallel_input
+    symm._POLICY = "1"
+    n, r = pm.PARALLEL_1D.world_size, pm.PARALLEL_1D.local_rank
+    dev = torch.device("cuda", torch.cuda.current_device())
+    torch.manual_seed(1)
+    B, S, H = 8, 256, 512
+    set_parallel_input(False)
+    col = nn_.Linear(H, 4 * H, activation="gelu", sequence_parallel=True).to(dev)
+    row = nn_.Linear(4 * H, H, sequence_parallel=True).to(dev)
+    W1, b1 = torch.randn(4 * H, H, device=dev) * 0.05, torch.randn(4 * H, device=dev) * 0.1
+    W2, b2 = torch.randn(H, 4 * H, device=dev) * 0.05, torch.randn(H, device=dev) * 0.1
+    x0 = torch.randn(B, S, H, device=dev)
+    g0 = torch.randn(B, S, H, device=dev)
+    for t in (W1, b1, W2, b2, x0, g0):
+        dist.broadcast(t, src=0)
+    with torch.no_grad():
+        col.weight.copy_(W1.chunk(n, 0)[r]), col.bias.copy_(b1.chunk(n, 0)[r])
+        row.weight.copy_(W2.chunk(n, 1)[r]), row.bias.copy_(b2)
+    xr = x0.clone().requires_grad_(True)
+    W1r, b1r, W2r, b2r = (t.clone().requires_grad_(True) for t in (W1, b1, W2, b2))
+    yr = F.linear(F.gelu(F.linear(xr, W1r, b1r)), W2r, b2r)
+    yr.backward(g0)
+    before = symm_impl.STATS["gather_gemm_scatter"]
+    for rep in range(3):
+        for p in list(col.parameters()) + list(row.parameters()):
+            p.grad = None
+        x = x0.chunk(n, 0)[r].clone().requires_grad_(True)
+        with torch.autocast("cuda", dtype=torch.bfloat16):
+            y = row(col(x))
+        assert y.shape == (B // n, S, H)
+        y.backward(g0.chunk(n, 0)[r].to(y.dtype))
+        reduce_partial_grads(list(row.parameters()))
+        torch.cuda.synchronize()
+        ext.check_status()
+        assert _rel(y, yr.chunk(n, 0)[r]) < 2e-2, (rep, _rel(y, yr.chunk(n, 0)[r]))
+        assert _rel(x.grad, xr.grad.chunk(n, 0)[r]) < 2e-2
+        assert _rel(col.weight.grad, W1r.grad.chunk(n, 0)[r]) < 2e-2
+        assert _rel(row.weight.grad, W2r.grad.chunk(n, 1)[r]) < 2e-2
+        assert _rel(row.bias.grad, b2r.grad) < 2e-2 and _rel(col.bias.grad, b1r.grad.chunk(n, 0)[r]) < 2e-2
+    # 4 fused launches per round: gather->GEMM and GEMM->scatter forward, and their mirror images backward
+    assert symm_impl.STATS["gather_gemm_scatter"] - before == 12, symm_impl.STATS
+
+
 def _check_gpt2_step():
     from cubework_b200.engine import Trainer
     from cubework_b200.models import gpt2
@@ -233,6 +287,26 @@ def test_3d_models_bf16_eight_ranks():
 def test_1d_models_bf16_two_ranks():
     for family in ("gpt2", "opt", "vit"):
         _multi(_check_model_against_cpu_oracle, 2, tp="1d", args=(family, ))
+
+
+def test_1d_sequence_parallel_layers_two_ranks():
+    _multi(_check_sp_layers_bf16)
+
+
+def test_1d_sequence_parallel_layers_every_gpu():
+    n = torch.cuda.device_count()
+    if n < 4:
+        pytest.skip("needs at least 4 GPUs")
+    _multi(_check_sp_layers_bf16, 8 if n >= 8 else 4)
+
+
+def test_1d_sequence_parallel_gpt2_two_ranks():
+    """Tiny GPT-2 with row-sharded activations, fused kernels forced on, against the unsharded fp32 model."""
+    _multi(_check_model_against_cpu_oracle, 2, tp="1d", args=("gpt2_sp", True))
+
+
+def test_1d_sequence_parallel_gpt2_four_ranks():
+    _multi(_check_model_against_cpu_oracle, 4, tp="1d", args=("gpt2_sp", True))
 
 
 def test_fused_gemm_all_reduce_two_ranks():
