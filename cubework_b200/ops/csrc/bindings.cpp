@@ -77,8 +77,7 @@ static int act_code(const std::string& a) {
 
 // C = act(op(A) op(B) + bias); returns (C, Z) with Z the pre-activation tensor when requested.
 std::vector<torch::Tensor> gemm(torch::Tensor a, torch::Tensor b, bool trans_a, bool trans_b,
-                                c10::optional<torch::Tensor> bias, const std::string& act, bool out_f32, bool want_z,
-                                int64_t force_bn, int64_t force_splits, int64_t mn_lbo, int64_t mn_sbo) {
+                                c10::optional<torch::Tensor> bias, const std::string& act, bool out_f32, bool want_z) {
   TORCH_CHECK(a.is_cuda() && b.is_cuda() && a.dim() == 2 && b.dim() == 2 && a.is_contiguous() && b.is_contiguous());
   TORCH_CHECK(a.scalar_type() == b.scalar_type() &&
               (a.scalar_type() == torch::kBFloat16 || a.scalar_type() == torch::kFloat16));
@@ -109,8 +108,6 @@ std::vector<torch::Tensor> gemm(torch::Tensor a, torch::Tensor b, bool trans_a, 
   g.out_f32 = out_f32;
   g.act = act_code(act);
   g.allow_split_k = g.act == kActNone && !want_z;
-  g.force_bn = static_cast<int>(force_bn); g.force_splits = static_cast<int>(force_splits);
-  g.mn_lbo = static_cast<uint32_t>(mn_lbo); g.mn_sbo = static_cast<uint32_t>(mn_sbo);
   g.num_sms = at::cuda::getCurrentDeviceProperties()->multiProcessorCount;
   g.status = g_status_dev;
   gemm_launch(g, at::cuda::getCurrentCUDAStream());

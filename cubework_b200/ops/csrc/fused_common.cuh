@@ -83,11 +83,6 @@ __device__ __forceinline__ void bulk_load(void* sdst, const void* gsrc, uint32_t
                : "memory");
 }
 __device__ __forceinline__ void bulk_wait_group_1() { asm volatile("cp.async.bulk.wait_group 1;" ::: "memory"); }
-__device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, const void* ssrc, int x, int y) {
-  asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];" ::"l"(map), "r"(smem_u32(ssrc)),
-               "r"(x), "r"(y)
-               : "memory");
-}
 __device__ __forceinline__ void worker_sync() { asm volatile("bar.sync 1, %0;" ::"n"(kWorkers) : "memory"); }
 
 // Staged tile layout (staging slots, result buffer, pull slots): two column halves of [128 rows][128 cols], so

@@ -91,8 +91,20 @@ struct GgsParams {
   // Row-block order of a product whose A operand is gathered along its rows (and is not scattered): this rank's
   // own rows first, then panel by panel over the other sources in the order their pushes arrive.
   int m_remap, m_rps;        // enabled; row blocks per source
+  long long* trace;          // optional [CTAs * 3][kGgsTraceLen][2] (event, globaltimer): performance debugging
   int* status;
 };
+
+// Event trace: three writers per CTA (0: TMA producer / push loader, 1: epilogue warp 0 / push storer, 2: MMA issuer).
+constexpr int kGgsTraceLen = 512;
+__device__ __forceinline__ void ggs_trace(long long* trace, int role, int& n, int code, int tile) {
+  if (trace != nullptr && n < kGgsTraceLen) {
+    long long* e = trace + ((static_cast<size_t>(blockIdx.x) * 3 + role) * kGgsTraceLen + n) * 2;
+    e[0] = (static_cast<long long>(code) << 32) | static_cast<unsigned>(tile);
+    e[1] = static_cast<long long>(globaltimer_ns());
+    ++n;
+  }
+}
 
 __device__ __forceinline__ void fence_proxy_async_all() { asm volatile("fence.proxy.async;" ::: "memory"); }
 template <int N>
@@ -279,6 +291,10 @@ gather_gemm_scatter_kernel(const __grid_constant__ CUtensorMap tma_a, const __gr
   const int lane = threadIdx.x & 31;
   const int kb_total = (p.K + kBK - 1) / kBK;
   const bool is_comm = static_cast<int>(blockIdx.x) < p.num_comm_ctas;
+  if (p.trace != nullptr && threadIdx.x == 32 * 3 + 1) {      // a thread with no other role: entry stamp of the CTA
+    int n0 = kGgsTraceLen - 2;
+    ggs_trace(p.trace, 0, n0, 30, 0);
+  }
 
   if (is_comm) {
     // =========================================================== communication CTA: push this rank's shards
@@ -338,6 +354,8 @@ gather_gemm_scatter_kernel(const __grid_constant__ CUtensorMap tma_a, const __gr
     int seq = -1;                                   // storer: index of the bulk group committed last
     int box_tail = 0;
     bool ok = true;
+    int ntr = 0;
+    ggs_trace(p.trace, warp, ntr, 20, 0);
     for (int i = c; i < n_first + n_second && ok; i += p.num_comm_ctas) {
       const bool is_second = i >= n_first;
       const GatherPush& op = is_second ? second : first;
@@ -367,7 +385,9 @@ gather_gemm_scatter_kernel(const __grid_constant__ CUtensorMap tma_a, const __gr
       if (warp == 1 && ok) {
         // the panel is complete at its destination: hand its flag to the publisher (the loader keeps prefetching
         // the next panel into free slots meanwhile)
+        ggs_trace(p.trace, 1, ntr, 21, i);
         bulk_wait_group0();
+        ggs_trace(p.trace, 1, ntr, 22, i);
         for (int spin = 0; box_tail - box.head >= kPendItems * 2 && spin < (1 << 22); ++spin) __nanosleep(50);
         int* f = op.flags[dest] + op.me * op.panels + panel;
         box.item[box_tail % (kPendItems * 2)] =
@@ -456,12 +476,15 @@ gather_gemm_scatter_kernel(const __grid_constant__ CUtensorMap tma_a, const __gr
       int owner, li;
       Known ka{known_a, 0, p.va.live ? (p.va.n - p.va.own_direct) * p.va.panels : 0};
       Known kb_{known_b, 0, p.vb.live ? (p.vb.n - p.vb.own_direct) * p.vb.panels : 0};
+      int ntr = 0;
       for (int k = 0; !*abort_flag && tile_of(k, owner, li); ++k) {
         const TileInfo ti = tile_info(p, owner, li, kb_total);
         OperandTile<A_KMAJOR, kBM / 64> ta;
         OperandTile<B_KMAJOR, BN / 64> tb;
+        ggs_trace(p.trace, 0, ntr, 1, li);
         bool ok = begin_tile(p.va, ka, ti.row0, kBM, p.k_start, ta, p.status) &&
                   begin_tile(p.vb, kb_, ti.col0, BN, p.k_start, tb, p.status);
+        ggs_trace(p.trace, 0, ntr, 2, li);
         if (!ok) { *abort_flag = 1; break; }
         int kb = p.k_start;
         for (int kbi = 0; kbi < kb_total; ++kbi) {
@@ -497,11 +520,14 @@ gather_gemm_scatter_kernel(const __grid_constant__ CUtensorMap tma_a, const __gr
       uint32_t phase = 0;
       int it = 0;
       int owner, li;
+      int ntr = 0;
       for (int k = 0; !*abort_flag && tile_of(k, owner, li); ++k) {
         const int acc = it & 1;
         const uint32_t acc_phase = (it >> 1) & 1;
         ++it;
+        ggs_trace(p.trace, 2, ntr, 10, li);
         if (!mbar_wait(&tempty_bar[acc], acc_phase ^ 1, abort_flag, p.status, kErrTmemEmptyTimeout, li)) break;
+        ggs_trace(p.trace, 2, ntr, 11, li);
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + acc * BN;
         bool ok = true;
@@ -523,6 +549,7 @@ gather_gemm_scatter_kernel(const __grid_constant__ CUtensorMap tma_a, const __gr
         }
         if (!ok) break;
         tc_commit(&tfull_bar[acc]);
+        ggs_trace(p.trace, 2, ntr, 12, li);
       }
     }
   } else if (warp == kPublisherWarp) {
@@ -575,12 +602,16 @@ gather_gemm_scatter_kernel(const __grid_constant__ CUtensorMap tma_a, const __gr
     int it = 0;
     bool failed = false;
     int owner, li;
+    int ntr = 0;
+    const bool tr = quarter == 0 && lane == 0;
     for (int k = 0; !*abort_flag && !failed && tile_of(k, owner, li); ++k) {
       const TileInfo ti = tile_info(p, owner, li, kb_total);
       const int acc = it & 1;
       const uint32_t acc_phase = (it >> 1) & 1;
       ++it;
+      if (tr) ggs_trace(p.trace, 1, ntr, 3, li);
       if (!mbar_wait(&tfull_bar[acc], acc_phase, abort_flag, p.status, kErrTmemFullTimeout, li)) break;
+      if (tr) ggs_trace(p.trace, 1, ntr, 4, li);
       tc_fence_after();
       const bool mine = !push_role;
       const InT* stage = reinterpret_cast<const InT*>(p.stage[scat ? p.sme : 0]) + static_cast<size_t>(li) * p.sn * kTileElems;
@@ -595,6 +626,7 @@ gather_gemm_scatter_kernel(const __grid_constant__ CUtensorMap tma_a, const __gr
             ok = wait_flag(p.sflags[p.sme] + (static_cast<size_t>(li) * p.sn + lane) * 8 + quarter * 2 + h, p.sepoch,
                            p.status, li);
           if (__any_sync(0xffffffffu, !ok)) { failed = true; break; }
+          if (tr) ggs_trace(p.trace, 1, ntr, 5, li * 2 + h);
         }
         __syncwarp();
 #pragma unroll 1
@@ -634,7 +666,7 @@ gather_gemm_scatter_kernel(const __grid_constant__ CUtensorMap tma_a, const __gr
                 store_row<InT>(reinterpret_cast<InT*>(p.z_out) + o, v, (p.ldo % 8 == 0) && c0 + 32 <= ti.cols, ti.cols - c0);
               if (p.act == kActGelu) {
 #pragma unroll
-                for (int j = 0; j < 32; ++j) v[j] = gelu_f(v[j]);
+                for (int j = 0; j < 32; ++j) v[j] = gelu_fast(v[j]);
               } else if (p.act == kActRelu) {
 #pragma unroll
                 for (int j = 0; j < 32; ++j) v[j] = fmaxf(v[j], 0.f);
@@ -670,6 +702,7 @@ gather_gemm_scatter_kernel(const __grid_constant__ CUtensorMap tma_a, const __gr
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&tempty_bar[acc]);
+      if (tr) ggs_trace(p.trace, 1, ntr, 6, li);
     }
     if (failed) *abort_flag = 1;
     if (lane == 0) {
@@ -688,6 +721,10 @@ gather_gemm_scatter_kernel(const __grid_constant__ CUtensorMap tma_a, const __gr
   if (warp == 1) {
     tc_fence_after();
     tmem_dealloc(tmem_base, Cfg::kTmemCols);
+  }
+  if (p.trace != nullptr && threadIdx.x == 32 * 3 + 1) {
+    int n1 = kGgsTraceLen - 1;
+    ggs_trace(p.trace, 0, n1, 31, 0);
   }
 }
 
@@ -752,7 +789,8 @@ static void gather_gemm_scatter(torch::Tensor a, torch::Tensor b, bool trans_a, 
                                 std::vector<int64_t> ga_bufs, std::vector<int64_t> ga_flags, std::vector<int64_t> gb,
                                 std::vector<int64_t> gb_bufs, std::vector<int64_t> gb_flags, std::vector<int64_t> sc,
                                 std::vector<int64_t> sc_stage, std::vector<int64_t> sc_flags, int64_t num_comm_ctas,
-                                int64_t status_ptr, int64_t act, c10::optional<torch::Tensor> z_out) {
+                                int64_t status_ptr, int64_t act, c10::optional<torch::Tensor> z_out,
+                                c10::optional<torch::Tensor> trace) {
   TORCH_CHECK(a.is_cuda() && b.is_cuda() && a.dim() == 2 && b.dim() == 2 && a.is_contiguous() && b.is_contiguous());
   TORCH_CHECK(a.scalar_type() == b.scalar_type() && out.is_contiguous() && out.dim() == 2);
   TORCH_CHECK(a.scalar_type() == torch::kBFloat16 || a.scalar_type() == torch::kFloat16);
@@ -830,6 +868,13 @@ static void gather_gemm_scatter(torch::Tensor a, torch::Tensor b, bool trans_a, 
     TORCH_CHECK(z_out->scalar_type() == a.scalar_type() && z_out->is_contiguous() && z_out->sizes() == out.sizes(),
                 "pre-activation output must match the output's shape and the operands' dtype");
     p.z_out = z_out->data_ptr();
+  }
+  p.trace = nullptr;
+  if (trace.has_value() && trace->defined()) {
+    TORCH_CHECK(trace->scalar_type() == torch::kInt64 && trace->is_contiguous() &&
+                trace->numel() >= static_cast<int64_t>(at::cuda::getCurrentDeviceProperties()->multiProcessorCount) * 3 *
+                                      kGgsTraceLen * 2, "trace tensor too small");
+    p.trace = reinterpret_cast<long long*>(trace->data_ptr<int64_t>());
   }
   p.m_remap = 0; p.m_rps = 0;
   if (p.va.live && p.va.g == 0 && ak && p.sc_dim < 0 && p.va.own_direct && p.va.panel_rows == kBM &&

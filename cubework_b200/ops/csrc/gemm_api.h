@@ -19,8 +19,6 @@ struct GemmArgs {
   bool out_f32 = false;
   int act = kActNone;
   bool allow_split_k = true;
-  int force_bn = 0, force_splits = 0;
-  uint32_t mn_lbo = 0, mn_sbo = 0;
   int num_sms = 148;
   int* status = nullptr;
 };

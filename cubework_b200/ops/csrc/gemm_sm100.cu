@@ -5,8 +5,12 @@
 // * warp 0   : TMA producer (one lane), kStages-deep ring of {A tile 128xBK, B tile BNxBK}
 // * warp 1   : MMA issuer (one lane) + TMEM owner; two accumulators (2*BN columns) so the epilogue of
 //              tile i overlaps the main loop of tile i+1
-// * warps 2-5: epilogue, one TMEM lane quarter each: tcgen05.ld -> bias / GELU / ReLU -> 16-byte stores,
-//              optionally also the pre-activation value, or fp32 `red.add` for split-K
+// * warps 2-9: epilogue, two warps per TMEM lane quarter (one per half of the tile's columns): tcgen05.ld of
+//              128 bytes of output per row -> bias / GELU / ReLU -> a 32-row x 128-byte staging block in shared
+//              memory (128-byte swizzle, bank-conflict free) -> one TMA tile store (or TMA reduce-add in fp32
+//              for split-K), which writes whole 128-byte lines and clips at the matrix edge.  The accumulator
+//              is handed back to the MMA warp as soon as its last column has been read.  Outputs whose row
+//              pitch is not a multiple of 16 bytes take a direct-store path instead.
 //
 // Both operands may be K-major (row-major [rows, K]) or MN-major (row-major [K, rows]); the four
 // combinations cover forward (X * W^T), data gradient (dY * W) and weight gradient (dY^T * X) without any
@@ -64,6 +68,24 @@ CUtensorMap make_tma_2d_plain(const void* ptr, uint64_t rows, uint64_t cols, uin
   return m;
 }
 
+// 2-D map for epilogue tile stores: row-major [rows, cols] of 2- or 4-byte elements, box = 128 bytes x 32 rows,
+// 128-byte swizzle (the staging block in shared memory is written in that pattern).
+CUtensorMap make_tma_2d_store(const void* ptr, uint64_t rows, uint64_t cols, uint64_t ld, int elem_bytes, bool is_bf16) {
+  TORCH_CHECK((reinterpret_cast<uintptr_t>(ptr) & 15) == 0 && (ld * elem_bytes) % 16 == 0,
+              "TMA store target must be 16-byte aligned with a 16-byte multiple row pitch");
+  CUtensorMap m;
+  cuuint64_t dims[2] = {cols, rows};
+  cuuint64_t strides[1] = {ld * static_cast<uint64_t>(elem_bytes)};
+  cuuint32_t box[2] = {static_cast<cuuint32_t>(128 / elem_bytes), 32};
+  cuuint32_t estr[2] = {1, 1};
+  const CUtensorMapDataType dt = elem_bytes == 4 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32
+                                                 : (is_bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16);
+  CUresult r = get_encode()(&m, dt, 2, const_cast<void*>(ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                            CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  TORCH_CHECK(r == CUDA_SUCCESS, "cuTensorMapEncodeTiled (store) failed with code ", static_cast<int>(r));
+  return m;
+}
+
 // 4-D map over 16-bit data [d3][d2][d1][d0] (d0 innermost, strides in bytes for d1..d3), box = 64 x 128 x 1 x 1.
 // Reads past any extent are zero-filled, which is how tiles get their padding.
 CUtensorMap make_tma_4d(const void* ptr, uint64_t d0, uint64_t d1, uint64_t d2, uint64_t d3, uint64_t s1, uint64_t s2,
@@ -83,12 +105,14 @@ CUtensorMap make_tma_4d(const void* ptr, uint64_t d0, uint64_t d1, uint64_t d2, 
 }
 
 template <int BN, bool A_KMAJOR, bool B_KMAJOR, typename InT, bool OUT_F32>
-__global__ void __launch_bounds__(kGemmThreads, 1)
-gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b, GemmParams p) {
-  using Cfg = GemmCfg<BN>;
+__global__ void __launch_bounds__(kGemmThreadsV2, 1)
+gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
+            const __grid_constant__ CUtensorMap tma_out, const __grid_constant__ CUtensorMap tma_z, GemmParams p) {
+  using Cfg = GemmCfgV2<BN>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + Cfg::kStages * Cfg::kStageBytes);
+  uint8_t* stage_out = smem + Cfg::kStages * Cfg::kStageBytes;                     // 8 x 4 KB, 1024-byte aligned
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(stage_out + kEpiWarps * kEpiBlockBytes);
   uint64_t* empty_bar = full_bar + Cfg::kStages;
   uint64_t* tfull_bar = empty_bar + Cfg::kStages;
   uint64_t* tempty_bar = tfull_bar + 2;
@@ -105,12 +129,16 @@ gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ C
     }
     for (int a = 0; a < 2; ++a) {
       mbar_init(&tfull_bar[a], 1);
-      mbar_init(&tempty_bar[a], 4);
+      mbar_init(&tempty_bar[a], kEpiWarps);
     }
     *abort_flag = 0;
     fence_barrier_init();
     tma_prefetch_desc(&tma_a);
     tma_prefetch_desc(&tma_b);
+    if (p.tma_store) {
+      tma_prefetch_desc(&tma_out);
+      if (p.z_out != nullptr) tma_prefetch_desc(&tma_z);
+    }
   }
   if (warp == 1) {
     tmem_alloc(tmem_slot, Cfg::kTmemCols);
@@ -182,9 +210,9 @@ gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ C
 #pragma unroll
           for (int k16 = 0; k16 < kBK / 16; ++k16) {
             const uint64_t da = A_KMAJOR ? make_smem_desc(sa + k16 * 32, 16, 1024)
-                                         : make_smem_desc(sa + k16 * 2048, p.mn_lbo, p.mn_sbo);
+                                         : make_smem_desc(sa + k16 * 2048, kGemmMnLbo, kGemmMnSbo);
             const uint64_t db = B_KMAJOR ? make_smem_desc(sb + k16 * 32, 16, 1024)
-                                         : make_smem_desc(sb + k16 * 2048, p.mn_lbo, p.mn_sbo);
+                                         : make_smem_desc(sb + k16 * 2048, kGemmMnLbo, kGemmMnSbo);
             tc_mma_f16(d_tmem, da, db, idesc, (kb > kb0 || k16 > 0) ? 1u : 0u);
           }
           tc_commit(&empty_bar[stage]);   // frees the stage once these MMAs have consumed it
@@ -195,12 +223,17 @@ gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ C
       }
     }
   } else {
-    // ------------------------------------------------------------------ epilogue (4 warps)
-    const int quarter = warp & 3;           // TMEM lanes [32*quarter, 32*quarter + 32)
+    // ------------------------------------------------------------------ epilogue (8 warps)
     using OutT = typename OutType<InT, OUT_F32>::type;
+    const int ew = warp - 2;                 // 0..7
+    const int quarter = warp & 3;            // TMEM lanes [32*quarter, 32*quarter + 32) (fixed by the hardware)
+    const int half = ew >> 2;                // which half of the tile's columns
+    constexpr int kHalfCols = BN / 2;
+    constexpr int kChunk = 128 / static_cast<int>(sizeof(OutT));   // columns per 128-byte staging row
+    constexpr int kLoads = kChunk / 32;                            // tcgen05.ld (32 columns) per chunk
+    uint8_t* sbuf = stage_out + ew * kEpiBlockBytes;
     OutT* out = reinterpret_cast<OutT*>(p.out);
     InT* zout = reinterpret_cast<InT*>(p.z_out);
-    const bool vec_ok = (p.ldo % (16 / sizeof(OutT)) == 0) && ((reinterpret_cast<uintptr_t>(p.out) & 15) == 0);
     int it = 0;
     for (int w = blockIdx.x; w < total_work && !*abort_flag; w += gridDim.x, ++it) {
       int tile_m, tile_n, kb0, kb1;
@@ -209,46 +242,115 @@ gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ C
       const uint32_t acc_phase = (it >> 1) & 1;
       if (!mbar_wait(&tfull_bar[acc], acc_phase, abort_flag, p.status, kErrTmemFullTimeout, w)) break;
       tc_fence_after();
-      const int row = tile_m * kBM + quarter * 32 + lane;
-      const bool row_ok = row < p.M;
+      const int row0 = tile_m * kBM + quarter * 32;
+      const int row = row0 + lane;
       const bool add_bias = p.bias != nullptr && kb0 == 0;   // split-K: only the first split adds it
+      const uint32_t t_addr = tmem_base + acc * BN + half * kHalfCols + (static_cast<uint32_t>(quarter * 32) << 16);
+      const int colbase = tile_n * BN + half * kHalfCols;
+      if (p.tma_store) {
 #pragma unroll 1
-      for (int c = 0; c < BN / 32; ++c) {
-        const int col0 = tile_n * BN + c * 32;
-        if (col0 >= p.N) break;             // warp-uniform
-        uint32_t r[32];
-        tmem_ld_32x32(tmem_base + acc * BN + c * 32 + (static_cast<uint32_t>(quarter * 32) << 16), r);
-        tmem_wait_ld();
-        float v[32];
+        for (int c = 0; c < kHalfCols / kChunk; ++c) {
+          const int col0 = colbase + c * kChunk;
+          const bool live = col0 < p.N;       // warp-uniform; dead chunks are still read so the hand-back below is uniform
+          float v[kChunk];
+          {
+            uint32_t r0[32];
+            tmem_ld_32x32(t_addr + c * kChunk, r0);
+            if constexpr (kLoads == 2) {
+              uint32_t r1[32];
+              tmem_ld_32x32(t_addr + c * kChunk + 32, r1);
+              tmem_wait_ld();
 #pragma unroll
-        for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
-        const bool full_chunk = col0 + 32 <= p.N;
-        if (add_bias) {
+              for (int j = 0; j < 32; ++j) v[32 + j] = __uint_as_float(r1[j]);
+            } else {
+              tmem_wait_ld();
+            }
 #pragma unroll
-          for (int j = 0; j < 32; ++j)
-            if (full_chunk || col0 + j < p.N) v[j] += __ldg(p.bias + col0 + j);
-        }
-        if (row_ok) {
-          if (p.z_out != nullptr) store_row<InT>(zout + static_cast<size_t>(row) * p.ldo + col0, v, full_chunk && vec_ok, p.N - col0);
+            for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r0[j]);
+          }
+          if (c == kHalfCols / kChunk - 1) {
+            // every column of this warp's part has been read: the MMA warp may overwrite the accumulator
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&tempty_bar[acc]);
+          }
+          if (!live) continue;
+          if (add_bias) {
+#pragma unroll
+            for (int j = 0; j < kChunk; ++j) v[j] += (col0 + j < p.N) ? __ldg(p.bias + col0 + j) : 0.f;
+          }
+          if constexpr (!OUT_F32) {
+            if (p.z_out != nullptr) {
+              if (lane == 0) bulk_wait_group_read0();
+              __syncwarp();
+              stage_row_16bit<InT>(sbuf, lane, v);
+              fence_proxy_async();
+              __syncwarp();
+              if (lane == 0) {
+                tma_store_2d(&tma_z, sbuf, col0, row0);
+                bulk_commit_group();
+              }
+            }
+          }
           if (p.act == kActGelu) {
 #pragma unroll
-            for (int j = 0; j < 32; ++j) v[j] = gelu_f(v[j]);
+            for (int j = 0; j < kChunk; ++j) v[j] = gelu_fast(v[j]);
           } else if (p.act == kActRelu) {
 #pragma unroll
-            for (int j = 0; j < 32; ++j) v[j] = fmaxf(v[j], 0.f);
+            for (int j = 0; j < kChunk; ++j) v[j] = fmaxf(v[j], 0.f);
           }
-          OutT* dst = out + static_cast<size_t>(row) * p.ldo + col0;
-          if (OUT_F32 && p.splits > 1) {
-            red_row(reinterpret_cast<float*>(dst), v, full_chunk && vec_ok, p.N - col0);
-          } else {
-            store_row<OutT>(dst, v, full_chunk && vec_ok, p.N - col0);
+          if (lane == 0) bulk_wait_group_read0();       // the previous store of this warp has finished reading sbuf
+          __syncwarp();
+          if constexpr (OUT_F32) stage_row_f32(sbuf, lane, v);
+          else stage_row_16bit<InT>(sbuf, lane, v);
+          fence_proxy_async();
+          __syncwarp();
+          if (lane == 0) {
+            if (OUT_F32 && p.splits > 1) tma_reduce_add_2d(&tma_out, sbuf, col0, row0);
+            else tma_store_2d(&tma_out, sbuf, col0, row0);
+            bulk_commit_group();
+          }
+        }
+      } else {
+        // direct stores: row pitch or base not 16-byte aligned
+        const bool row_ok = row < p.M;
+#pragma unroll 1
+        for (int c = 0; c < kHalfCols / 32; ++c) {
+          const int col0 = colbase + c * 32;
+          uint32_t r[32];
+          tmem_ld_32x32(t_addr + c * 32, r);
+          tmem_wait_ld();
+          if (c == kHalfCols / 32 - 1) {
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&tempty_bar[acc]);
+          }
+          if (col0 >= p.N) continue;
+          float v[32];
+#pragma unroll
+          for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
+          if (add_bias) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j)
+              if (col0 + j < p.N) v[j] += __ldg(p.bias + col0 + j);
+          }
+          if (row_ok) {
+            if (p.z_out != nullptr) store_row<InT>(zout + static_cast<size_t>(row) * p.ldo + col0, v, false, p.N - col0);
+            if (p.act == kActGelu) {
+#pragma unroll
+              for (int j = 0; j < 32; ++j) v[j] = gelu_fast(v[j]);
+            } else if (p.act == kActRelu) {
+#pragma unroll
+              for (int j = 0; j < 32; ++j) v[j] = fmaxf(v[j], 0.f);
+            }
+            OutT* dst = out + static_cast<size_t>(row) * p.ldo + col0;
+            if (OUT_F32 && p.splits > 1) red_row(reinterpret_cast<float*>(dst), v, false, p.N - col0);
+            else store_row<OutT>(dst, v, false, p.N - col0);
           }
         }
       }
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&tempty_bar[acc]);
     }
+    if (lane == 0) bulk_wait_group0();     // the tile stores must have left shared memory (and landed) before exit
   }
 
   // ---------------------------------------------------------------------- teardown
@@ -265,32 +367,33 @@ gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ C
 }
 
 template <int BN, bool AK, bool BK_, typename InT, bool OUT_F32>
-static void launch(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p, int grid, cudaStream_t stream) {
-  using Cfg = GemmCfg<BN>;
+static void launch(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& to, const CUtensorMap& tz,
+                   const GemmParams& p, int grid, cudaStream_t stream) {
+  using Cfg = GemmCfgV2<BN>;
   auto kern = gemm_kernel<BN, AK, BK_, InT, OUT_F32>;
   static bool configured = false;
   if (!configured) {
     C10_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes));
     configured = true;
   }
-  kern<<<grid, kGemmThreads, Cfg::kSmemBytes, stream>>>(ta, tb, p);
+  kern<<<grid, kGemmThreadsV2, Cfg::kSmemBytes, stream>>>(ta, tb, to, tz, p);
   C10_CUDA_KERNEL_LAUNCH_CHECK();
 }
 
 template <int BN, typename InT, bool OUT_F32>
-static void dispatch_major(bool ak, bool bk, const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p, int grid,
-                           cudaStream_t s) {
-  if (ak && bk) launch<BN, true, true, InT, OUT_F32>(ta, tb, p, grid, s);
-  else if (ak && !bk) launch<BN, true, false, InT, OUT_F32>(ta, tb, p, grid, s);
-  else if (!ak && bk) launch<BN, false, true, InT, OUT_F32>(ta, tb, p, grid, s);
-  else launch<BN, false, false, InT, OUT_F32>(ta, tb, p, grid, s);
+static void dispatch_major(bool ak, bool bk, const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& to,
+                           const CUtensorMap& tz, const GemmParams& p, int grid, cudaStream_t s) {
+  if (ak && bk) launch<BN, true, true, InT, OUT_F32>(ta, tb, to, tz, p, grid, s);
+  else if (ak && !bk) launch<BN, true, false, InT, OUT_F32>(ta, tb, to, tz, p, grid, s);
+  else if (!ak && bk) launch<BN, false, true, InT, OUT_F32>(ta, tb, to, tz, p, grid, s);
+  else launch<BN, false, false, InT, OUT_F32>(ta, tb, to, tz, p, grid, s);
 }
 
 // Host entry.  a: [M,K] (trans_a=false) or [K,M]; b: [K,N] (trans_b=false) or [N,K]; both contiguous 2-D.
 void gemm_launch(const GemmArgs& g, cudaStream_t stream) {
   const bool a_kmajor = !g.trans_a;
   const bool b_kmajor = g.trans_b;
-  const int bn = g.force_bn > 0 ? g.force_bn : ((g.N <= 128 || (g.N % 256 != 0 && g.N % 256 <= 128 && g.N < 1024)) ? 128 : 256);
+  const int bn = ((g.N <= 128 || (g.N % 256 != 0 && g.N % 256 <= 128 && g.N < 1024)) ? 128 : 256);
   const int tiles = ((g.M + kBM - 1) / kBM) * ((g.N + bn - 1) / bn);
   const int kb_total = (g.K + kBK - 1) / kBK;
   int sms = g.num_sms;
@@ -310,7 +413,6 @@ void gemm_launch(const GemmArgs& g, cudaStream_t stream) {
       if (eff >= 0.93) break;
     }
   }
-  if (g.force_splits > 0) splits = g.force_splits;
   {
     // no split may be empty: an accumulator that no MMA wrote holds stale TMEM contents
     const int per = (kb_total + splits - 1) / splits;
@@ -326,25 +428,33 @@ void gemm_launch(const GemmArgs& g, cudaStream_t stream) {
   p.M = g.M; p.N = g.N; p.K = g.K;
   p.out = g.out; p.z_out = g.z_out; p.bias = g.bias; p.ldo = g.N;
   p.act = g.act; p.splits = splits; p.is_bf16 = g.is_bf16 ? 1 : 0;
-  p.mn_lbo = g.mn_lbo > 0 ? g.mn_lbo : 8192;
-  p.mn_sbo = g.mn_sbo > 0 ? g.mn_sbo : 1024;
   p.status = g.status;
+  // tile stores through TMA need a 16-byte aligned base and row pitch; anything else takes the direct-store path
+  const int out_bytes = g.out_f32 ? 4 : 2;
+  const bool out_ok = (reinterpret_cast<uintptr_t>(g.out) & 15) == 0 && (static_cast<size_t>(g.N) * out_bytes) % 16 == 0;
+  const bool z_ok = g.z_out == nullptr || ((reinterpret_cast<uintptr_t>(g.z_out) & 15) == 0 && (static_cast<size_t>(g.N) * 2) % 16 == 0);
+  p.tma_store = (out_ok && z_ok) ? 1 : 0;
+  CUtensorMap to = ta, tz = ta;      // placeholders when unused
+  if (p.tma_store) {
+    to = make_tma_2d_store(g.out, g.M, g.N, g.N, out_bytes, g.is_bf16);
+    if (g.z_out != nullptr) tz = make_tma_2d_store(g.z_out, g.M, g.N, g.N, 2, g.is_bf16);
+  }
   const int grid = std::min(tiles * splits, sms);
   if (g.is_bf16) {
     if (bn == 256) {
-      if (g.out_f32) dispatch_major<256, __nv_bfloat16, true>(a_kmajor, b_kmajor, ta, tb, p, grid, stream);
-      else dispatch_major<256, __nv_bfloat16, false>(a_kmajor, b_kmajor, ta, tb, p, grid, stream);
+      if (g.out_f32) dispatch_major<256, __nv_bfloat16, true>(a_kmajor, b_kmajor, ta, tb, to, tz, p, grid, stream);
+      else dispatch_major<256, __nv_bfloat16, false>(a_kmajor, b_kmajor, ta, tb, to, tz, p, grid, stream);
     } else {
-      if (g.out_f32) dispatch_major<128, __nv_bfloat16, true>(a_kmajor, b_kmajor, ta, tb, p, grid, stream);
-      else dispatch_major<128, __nv_bfloat16, false>(a_kmajor, b_kmajor, ta, tb, p, grid, stream);
+      if (g.out_f32) dispatch_major<128, __nv_bfloat16, true>(a_kmajor, b_kmajor, ta, tb, to, tz, p, grid, stream);
+      else dispatch_major<128, __nv_bfloat16, false>(a_kmajor, b_kmajor, ta, tb, to, tz, p, grid, stream);
     }
   } else {
     if (bn == 256) {
-      if (g.out_f32) dispatch_major<256, __half, true>(a_kmajor, b_kmajor, ta, tb, p, grid, stream);
-      else dispatch_major<256, __half, false>(a_kmajor, b_kmajor, ta, tb, p, grid, stream);
+      if (g.out_f32) dispatch_major<256, __half, true>(a_kmajor, b_kmajor, ta, tb, to, tz, p, grid, stream);
+      else dispatch_major<256, __half, false>(a_kmajor, b_kmajor, ta, tb, to, tz, p, grid, stream);
     } else {
-      if (g.out_f32) dispatch_major<128, __half, true>(a_kmajor, b_kmajor, ta, tb, p, grid, stream);
-      else dispatch_major<128, __half, false>(a_kmajor, b_kmajor, ta, tb, p, grid, stream);
+      if (g.out_f32) dispatch_major<128, __half, true>(a_kmajor, b_kmajor, ta, tb, to, tz, p, grid, stream);
+      else dispatch_major<128, __half, false>(a_kmajor, b_kmajor, ta, tb, to, tz, p, grid, stream);
     }
   }
 }

@@ -84,7 +84,7 @@ def _gemm_ok(a, b, trans_a, trans_b):
     return (a.shape[1] % 8 == 0 and b.shape[1] % 8 == 0 and a.data_ptr() % 16 == 0 and b.data_ptr() % 16 == 0)
 
 
-def gemm(a, b, trans_a, trans_b, bias, act, out_dtype, pre_act_out, **dbg):
+def gemm(a, b, trans_a, trans_b, bias, act, out_dtype, pre_act_out):
     a = a.contiguous()
     b = b.contiguous()
     out_f32 = out_dtype == torch.float32
@@ -99,9 +99,7 @@ def gemm(a, b, trans_a, trans_b, bias, act, out_dtype, pre_act_out, **dbg):
         y = torch.nn.functional.gelu(z) if act == "gelu" else torch.relu(z) if act == "relu" else z
         return (y.to(out_dtype), z.to(out_dtype)) if pre_act_out else y.to(out_dtype)
     _count(1)
-    out, z = require().gemm(a, b, bool(trans_a), bool(trans_b), bias, act or "", out_f32, bool(pre_act_out),
-                            dbg.get("force_bn", 0), dbg.get("force_splits", 0), dbg.get("mn_lbo", 0),
-                            dbg.get("mn_sbo", 0))
+    out, z = require().gemm(a, b, bool(trans_a), bool(trans_b), bias, act or "", out_f32, bool(pre_act_out))
     return (out, z) if pre_act_out else out
 
 

@@ -20,6 +20,7 @@ _DONE_CAP = 1 << 16          # tiles per call
 _COMM_CTAS = int(os.environ.get("CUBEWORK_B200_COMM_CTAS", "0"))
 STATS = {"gemm_all_reduce": 0, "gather_gemm_scatter": 0}     # fused launches issued by this process
 TRACE = None                  # optional int64 [148, 192, 2] CUDA tensor: per-CTA event trace of the next fused launches
+GGS_TRACE = None              # optional int64 [148 * 3, 512, 2] CUDA tensor: the same for the gather/scatter kernel
 
 
 class Workspace:
@@ -244,7 +245,8 @@ def fused_gather_gemm_scatter(a, b, trans_a, trans_b, gather_a, gather_b, scatte
     ext._count(1)
     STATS["gather_gemm_scatter"] += 1
     m.gather_gemm_scatter(a, b, bool(trans_a), bool(trans_b), bias, out, ga_cfg, ga_bufs, ga_flags, gb_cfg, gb_bufs,
-                          gb_flags, sc_cfg, sc_stage, sc_flags, _PUSH_CTAS, m.status_device_ptr(), _ACT_CODE[act], z)
+                          gb_flags, sc_cfg, sc_stage, sc_flags, _PUSH_CTAS, m.status_device_ptr(), _ACT_CODE[act], z,
+                          GGS_TRACE)
     from . import collective
     if collective._profiler is not None:
         moved = 0

@@ -41,30 +41,35 @@ def test_gemm_layouts(trans_a, trans_b, M, N, K, dtype):
 
 
 @pytest.mark.parametrize("act", [None, "gelu", "relu"])
-@pytest.mark.parametrize("bn", [128, 256])
-def test_gemm_epilogues(act, bn):
+@pytest.mark.parametrize("N", [776, 1000, 60])
+def test_gemm_epilogues(act, N):
+    """Bias, activation and the pre-activation copy through both tile widths (N = 776 takes 128-wide tiles, N = 1000
+    takes 256-wide ones) and through the direct-store path (N = 60: a row pitch that TMA cannot store)."""
     ops, ext = _ops()
     torch.manual_seed(1)
-    M, N, K = 520, 776, 264
+    M, K = 520, 264
     a = torch.randn(M, K, device=DEV, dtype=torch.bfloat16)
     b = torch.randn(N, K, device=DEV, dtype=torch.bfloat16)
     bias = torch.randn(N, device=DEV)
     z_ref = a.float() @ b.float().t() + bias
     y_ref = torch.nn.functional.gelu(z_ref) if act == "gelu" else torch.relu(z_ref) if act == "relu" else z_ref
-    y, z = ext.gemm(a, b, False, True, bias, act, torch.bfloat16, True, force_bn=bn)
+    y, z = ext.gemm(a, b, False, True, bias, act, torch.bfloat16, True)
     ext.check_status()
     assert _rel_err(z, z_ref) < 6e-3 and _rel_err(y, y_ref) < 6e-3
+    y32 = ext.gemm(a, b, False, True, bias, act, torch.float32, False)
+    assert _rel_err(y32, y_ref) < 1e-4
 
 
-@pytest.mark.parametrize("splits", [0, 2, 7])
-def test_gemm_split_k_weight_gradient_shape(splits):
+@pytest.mark.parametrize("tokens,out_f,in_f", [(4096, 200, 328), (8192, 1600, 1600), (2048, 72, 104)])
+def test_gemm_split_k_weight_gradient_shape(tokens, out_f, in_f):
+    """fp32 weight gradients: few tiles with a long K are split (8 ways / 3 ways for the first two shapes) and summed
+    by TMA reduce-add; the last shape's row pitch (416 bytes) is fine for TMA, its 72 x 104 output a single tile."""
     ops, ext = _ops()
     torch.manual_seed(2)
-    tokens, out_f, in_f = 4096, 200, 328
     dy = torch.randn(tokens, out_f, device=DEV, dtype=torch.bfloat16)
     x = torch.randn(tokens, in_f, device=DEV, dtype=torch.bfloat16)
     ref = dy.float().t() @ x.float()
-    dw = ext.gemm(dy, x, True, False, None, None, torch.float32, False, force_splits=splits)
+    dw = ext.gemm(dy, x, True, False, None, None, torch.float32, False)
     ext.check_status()
     assert _rel_err(dw, ref) < 1e-4
 
