@@ -17,10 +17,11 @@
 //    for the flags of the (source, panel) pairs the tile reads (remembered in a shared-memory bitmap
 //    afterwards), so tiles whose operands are local start at once.  The K loop starts at the k-blocks of the
 //    local shard.
-//  * with a reduce-scatter, tile ownership follows the output shard: "push" CTAs compute tiles of other
-//    owners and send the 16-bit partials into the owner's staging buffer (8 KB bulk copies, flags batched
-//    behind one system-scope fence by a publisher thread); "own" CTAs compute this rank's tiles, wait for
-//    the other ranks' partials, add them in fp32 to the accumulator (+ bias) and store the output shard.
+//  * with a reduce-scatter, tile ownership follows the output shard: every GEMM CTA first computes its share
+//    of the tiles of other owners and sends the 16-bit partials into the owner's staging buffer (4 KB bulk
+//    copies, flags batched behind one system-scope fence by a publisher thread), then its share of this
+//    rank's tiles, to whose accumulators it adds the other ranks' partials in fp32 (+ bias) before storing
+//    the output shard.
 // Gather and staging buffers are used in two halves that alternate with the call epoch: a rank can run at
 // most one call ahead of a peer (it needs that peer's data of the current call to finish), so the half
 // written now was last read two calls ago.  Flags hold epochs that only grow.  Every wait is bounded and
@@ -41,11 +42,43 @@ namespace py = pybind11;
 
 namespace cw {
 
+// Thread layout of a GEMM CTA: warp 0 TMA producer, warp 1 MMA issuer, warps 2-9 epilogue (two per TMEM lane
+// quarter, one per half of the tile's columns), warp 10 publisher of the flags of pushed partial tiles.
+constexpr int kGgsEpiWarps = 8;
+constexpr int kGgsThreads = 64 + 32 * kGgsEpiWarps + 32;
+constexpr int kGgsPublisherWarp = 2 + kGgsEpiWarps;
+constexpr int kGgsSmemBytes = kFusedStages * GemmCfg<kFusedBN>::kStageBytes + kGgsEpiWarps * kEpiBlockBytes + 256 + 1024;
+static_assert(kGgsSmemBytes <= 227 * 1024, "gather/scatter kernel exceeds the shared memory of one SM");
+
+// Staged partial tile (staging slots of the reduce-scatter): four column quarters of [128 rows][64 columns]; inside a
+// quarter a row is 128 bytes and its 16-byte chunk j sits at chunk j ^ (row & 7).  The 32 rows x 64 columns that
+// one epilogue warp produces per step are therefore 4 KB of contiguous memory in exactly the pattern of its
+// shared-memory staging block, and travel as one bulk copy; readers apply the same mapping.
+__device__ __forceinline__ int staged_off_v2(int r, int cq, int j) {      // element offset of chunk j (0..7)
+  return cq * (kBM * 64) + r * 64 + ((j ^ (r & 7)) << 3);
+}
+
+struct Mailbox8 {
+  volatile int item[kGgsEpiWarps][kMailboxDepth];   // (staging slot << 3) | (quarter << 1) | half
+  volatile int tail[kGgsEpiWarps];                  // written by epilogue warp e
+  volatile int head[kGgsEpiWarps];                  // written by the publisher
+  volatile int finished;                            // number of epilogue warps that have left their loop
+};
+__device__ __forceinline__ void mailbox8_put(Mailbox8* mb, int e, int& tail, int value) {
+  // the publisher may lag by one fence; wait (bounded) if the ring is full
+  for (int spin = 0; tail - mb->head[e] >= kMailboxDepth && spin < (1 << 22); ++spin) __nanosleep(50);
+  mb->item[e][tail % kMailboxDepth] = value;
+  __threadfence_block();
+  ++tail;
+  mb->tail[e] = tail;
+}
+
 constexpr int kKnownWords = 64;            // 2048 (source, panel) arrival bits per operand
 constexpr int kPiece = 32 * 1024;          // bytes per bulk copy of the gather pushers
 constexpr int kPushSlots = 6;              // shared-memory pieces in flight per communication CTA
 constexpr int kPendItems = 16;
-static_assert(kPushSlots * kPiece + 1024 + 256 <= kFusedSmemBytes, "push slots must fit the GEMM allocation");
+constexpr int kPushInflight = 12;          // bulk stores a communication CTA keeps in flight before it waits
+static_assert(kPushSlots * kPiece + 1024 + 256 <= kGgsSmemBytes, "push slots must fit the GEMM allocation");
 
 struct GatherView {          // how the TMA producer sees one operand
   int live;                  // 0: an ordinary local tensor, nothing to wait for
@@ -86,6 +119,7 @@ struct GgsParams {
   void* out;                 // local [Ms or M][ldo]
   int ldo;
   const float* bias;         // optional, indexed by output column
+  int tma_store;             // the output (and z_out) is written with TMA tile stores (16-byte aligned base and pitch)
   int act;                   // activation applied by the tile's owner after the bias (kActNone / Gelu / Relu)
   void* z_out;               // optional copy of the value before the activation, input dtype, same layout as `out`
   // Row-block order of a product whose A operand is gathered along its rows (and is not scattered): this rank's
@@ -277,9 +311,10 @@ __device__ __forceinline__ void next_kb(const GatherView& v, OperandTile<KMAJOR,
 }
 
 template <bool A_KMAJOR, bool B_KMAJOR, typename InT, bool OUT_F32>
-__global__ void __launch_bounds__(kFusedThreads, 1)
+__global__ void __launch_bounds__(kGgsThreads, 1)
 gather_gemm_scatter_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
                            const __grid_constant__ CUtensorMap tma_a_own, const __grid_constant__ CUtensorMap tma_b_own,
+                           const __grid_constant__ CUtensorMap tma_out, const __grid_constant__ CUtensorMap tma_z,
                            const __grid_constant__ GgsParams p) {
   constexpr int BN = kFusedBN;
   using Cfg = GemmCfg<BN>;
@@ -291,7 +326,7 @@ gather_gemm_scatter_kernel(const __grid_constant__ CUtensorMap tma_a, const __gr
   const int lane = threadIdx.x & 31;
   const int kb_total = (p.K + kBK - 1) / kBK;
   const bool is_comm = static_cast<int>(blockIdx.x) < p.num_comm_ctas;
-  if (p.trace != nullptr && threadIdx.x == 32 * 3 + 1) {      // a thread with no other role: entry stamp of the CTA
+  if (p.trace != nullptr && threadIdx.x == 32 * 3 + 1) {      // entry stamp of the CTA
     int n0 = kGgsTraceLen - 2;
     ggs_trace(p.trace, 0, n0, 30, 0);
   }
@@ -356,6 +391,20 @@ gather_gemm_scatter_kernel(const __grid_constant__ CUtensorMap tma_a, const __gr
     bool ok = true;
     int ntr = 0;
     ggs_trace(p.trace, warp, ntr, 20, 0);
+    // storer: panels whose last store has been committed but may still be in flight: (last group, flag) pairs
+    constexpr int kDone = 8;
+    int done_seq[kDone];
+    int* done_flag[kDone];
+    int done_head = 0, done_tail = 0;
+    auto hand_over = [&](int upto) {               // flags of the panels whose stores are complete -> publisher
+      while (done_head < done_tail && done_seq[done_head % kDone] <= upto) {
+        for (int spin = 0; box_tail - box.head >= kPendItems * 2 && spin < (1 << 22); ++spin) __nanosleep(50);
+        box.item[box_tail % (kPendItems * 2)] = done_flag[done_head % kDone];
+        __threadfence_block();
+        box.tail = ++box_tail;
+        ++done_head;
+      }
+    };
     for (int i = c; i < n_first + n_second && ok; i += p.num_comm_ctas) {
       const bool is_second = i >= n_first;
       const GatherPush& op = is_second ? second : first;
@@ -379,25 +428,30 @@ gather_gemm_scatter_kernel(const __grid_constant__ CUtensorMap tma_a, const __gr
           ++seq;
           bulk_wait_group_read_n<2>();              // groups <= seq-2 no longer read their slot: hand it back
           if (seq >= 2) mbar_arrive(&empty_bar[(slot + kPushSlots - 2) % kPushSlots]);
+          bulk_wait_group_n<kPushInflight>();       // groups <= seq-kPushInflight have landed at their destination
+          hand_over(seq - kPushInflight);
         }
         if (++slot == kPushSlots) { slot = 0; phase ^= 1; }
       }
       if (warp == 1 && ok) {
-        // the panel is complete at its destination: hand its flag to the publisher (the loader keeps prefetching
-        // the next panel into free slots meanwhile)
-        ggs_trace(p.trace, 1, ntr, 21, i);
-        bulk_wait_group0();
-        ggs_trace(p.trace, 1, ntr, 22, i);
-        for (int spin = 0; box_tail - box.head >= kPendItems * 2 && spin < (1 << 22); ++spin) __nanosleep(50);
+        // every store of the panel is committed; its flag goes to the publisher once they have landed, which the
+        // stores of the following panels reveal (no drain of the pipeline per panel)
+        if (done_tail - done_head == kDone) {
+          ggs_trace(p.trace, 1, ntr, 21, i);
+          bulk_wait_group0();
+          ggs_trace(p.trace, 1, ntr, 22, i);
+          hand_over(seq);
+        }
         int* f = op.flags[dest] + op.me * op.panels + panel;
-        box.item[box_tail % (kPendItems * 2)] =
-            reinterpret_cast<int*>(reinterpret_cast<uintptr_t>(f) | (is_second ? 1u : 0u));
-        __threadfence_block();
-        box.tail = ++box_tail;
+        done_seq[done_tail % kDone] = seq;
+        done_flag[done_tail % kDone] = reinterpret_cast<int*>(reinterpret_cast<uintptr_t>(f) | (is_second ? 1u : 0u));
+        ++done_tail;
       }
     }
     if (warp == 1) {
       bulk_wait_group0();
+      hand_over(seq);
+      ggs_trace(p.trace, 1, ntr, 22, 0);
       __threadfence_block();
       box.finished = 1;
     }
@@ -405,14 +459,14 @@ gather_gemm_scatter_kernel(const __grid_constant__ CUtensorMap tma_a, const __gr
   }
 
   // ================================================================= GEMM CTA
-  uint8_t* epi = smem + kFusedStages * Cfg::kStageBytes;
-  uint64_t* full_bar = reinterpret_cast<uint64_t*>(epi + kEpiBytes);
+  uint8_t* epi = smem + kFusedStages * Cfg::kStageBytes;         // 8 staging blocks of 4 KB, 1024-byte aligned
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(epi + kGgsEpiWarps * kEpiBlockBytes);
   uint64_t* empty_bar = full_bar + kFusedStages;
   uint64_t* tfull_bar = empty_bar + kFusedStages;
   uint64_t* tempty_bar = tfull_bar + 2;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty_bar + 2);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
-  __shared__ Mailbox mailbox;
+  __shared__ Mailbox8 mailbox;
   __shared__ uint32_t known_a[kKnownWords], known_b[kKnownWords];
   if (threadIdx.x == 0) {
     for (int s = 0; s < kFusedStages; ++s) {
@@ -421,16 +475,20 @@ gather_gemm_scatter_kernel(const __grid_constant__ CUtensorMap tma_a, const __gr
     }
     for (int a = 0; a < 2; ++a) {
       mbar_init(&tfull_bar[a], 1);
-      mbar_init(&tempty_bar[a], 4);
+      mbar_init(&tempty_bar[a], kGgsEpiWarps);
     }
     *abort_flag = 0;
-    for (int q = 0; q < 4; ++q) { mailbox.tail[q] = 0; mailbox.head[q] = 0; }
+    for (int q = 0; q < kGgsEpiWarps; ++q) { mailbox.tail[q] = 0; mailbox.head[q] = 0; }
     mailbox.finished = 0;
     fence_barrier_init();
     tma_prefetch_desc(&tma_a);
     tma_prefetch_desc(&tma_b);
     tma_prefetch_desc(&tma_a_own);
     tma_prefetch_desc(&tma_b_own);
+    if (p.tma_store) {
+      tma_prefetch_desc(&tma_out);
+      if (p.z_out != nullptr) tma_prefetch_desc(&tma_z);
+    }
   }
   if (threadIdx.x >= 32 && threadIdx.x < 32 + kKnownWords) {
     known_a[threadIdx.x - 32] = 0;
@@ -451,22 +509,34 @@ gather_gemm_scatter_kernel(const __grid_constant__ CUtensorMap tma_a, const __gr
   const int G = p.num_gemm_ctas;
   const int bid = blockIdx.x - p.num_comm_ctas;
   const int tpo = p.tiles_m * p.tiles_n;                     // tiles per owner
-  int g_push = 0;
-  if (scat) g_push = max(1, min(G - 1, (G * (p.sn - 1) + p.sn / 2) / p.sn));
-  const int g_own = G - g_push;
-  const bool push_role = bid < g_push;
+  // Tile order of a GEMM CTA under a reduce-scatter.  Tiles of other owners ("push": the partial leaves for its
+  // owner) and this rank's own tiles (the peers' partials are added) are interleaved: pushes keep the links busy
+  // from the first to the last tile while the own tiles' arithmetic and stores run in their shadow.  An own tile is
+  // taken only when this CTA is kLead pushes past the point where, by symmetry, the peers pushed their partials of
+  // that tile, so its flags are normally up when it looks (and waits cannot chain: every wait is for a push that
+  // was issued strictly earlier in the common order).  Without a reduce-scatter every tile is an own tile.
+  constexpr int kLead = 3;
   const int n_push_items = scat ? tpo * (p.sn - 1) : 0;
-  auto tile_of = [&](int k, int& owner, int& li) -> bool {   // false: finished
-    if (push_role) {
-      const int item = bid + k * g_push;
-      if (item >= n_push_items) return false;
-      li = item / (p.sn - 1);
-      owner = (p.sme + 1 + item % (p.sn - 1)) % p.sn;
+  const int np = bid < n_push_items ? (n_push_items - bid + G - 1) / G : 0;    // pushes of this CTA
+  const int own0 = (bid + G - n_push_items % G) % G;                            // round robin continues after the pushes
+  const int no = own0 < tpo ? (tpo - own0 + G - 1) / G : 0;                     // own tiles of this CTA
+  struct Sched { int ip, io; };
+  bool push_tile = false;
+  auto next_tile = [&](Sched& sc, int& owner, int& li) -> bool {              // false: finished; sets push_tile
+    if (sc.ip < np && (sc.io >= no || sc.ip < (sc.io + 1) * (p.sn - 1) + kLead)) {
+      const int v = bid + sc.ip * G;
+      ++sc.ip;
+      push_tile = true;
+      li = v / (p.sn - 1);
+      owner = (p.sme + 1 + v % (p.sn - 1)) % p.sn;
       return true;
     }
-    li = (bid - g_push) + k * g_own;
+    if (sc.io >= no) return false;
+    push_tile = false;
+    li = own0 + sc.io * G;
+    ++sc.io;
     owner = scat ? p.sme : 0;
-    return li < tpo;
+    return true;
   };
 
   if (warp == 0) {
@@ -477,7 +547,8 @@ gather_gemm_scatter_kernel(const __grid_constant__ CUtensorMap tma_a, const __gr
       Known ka{known_a, 0, p.va.live ? (p.va.n - p.va.own_direct) * p.va.panels : 0};
       Known kb_{known_b, 0, p.vb.live ? (p.vb.n - p.vb.own_direct) * p.vb.panels : 0};
       int ntr = 0;
-      for (int k = 0; !*abort_flag && tile_of(k, owner, li); ++k) {
+      Sched sched{0, 0};
+      while (!*abort_flag && next_tile(sched, owner, li)) {
         const TileInfo ti = tile_info(p, owner, li, kb_total);
         OperandTile<A_KMAJOR, kBM / 64> ta;
         OperandTile<B_KMAJOR, BN / 64> tb;
@@ -521,7 +592,8 @@ gather_gemm_scatter_kernel(const __grid_constant__ CUtensorMap tma_a, const __gr
       int it = 0;
       int owner, li;
       int ntr = 0;
-      for (int k = 0; !*abort_flag && tile_of(k, owner, li); ++k) {
+      Sched sched{0, 0};
+      while (!*abort_flag && next_tile(sched, owner, li)) {
         const int acc = it & 1;
         const uint32_t acc_phase = (it >> 1) & 1;
         ++it;
@@ -552,16 +624,17 @@ gather_gemm_scatter_kernel(const __grid_constant__ CUtensorMap tma_a, const __gr
         ggs_trace(p.trace, 2, ntr, 12, li);
       }
     }
-  } else if (warp == kPublisherWarp) {
+  } else if (warp == kGgsPublisherWarp) {
     if (lane == 0 && scat) {
       // ---- publisher of the partial tiles this CTA pushed: one system-scope fence per batch, then the flags
-      int head[4] = {0, 0, 0, 0};
+      int head[kGgsEpiWarps];
+      for (int q = 0; q < kGgsEpiWarps; ++q) head[q] = 0;
       const unsigned long long t_start = globaltimer_ns();
       for (;;) {
         int batch[32];
         int nb = 0;
         const int fin = mailbox.finished;
-        for (int q = 0; q < 4; ++q) {
+        for (int q = 0; q < kGgsEpiWarps; ++q) {
           const int tail = mailbox.tail[q];
           while (head[q] < tail && nb < 32) {
             batch[nb++] = mailbox.item[q][head[q] % kMailboxDepth];
@@ -570,9 +643,9 @@ gather_gemm_scatter_kernel(const __grid_constant__ CUtensorMap tma_a, const __gr
           mailbox.head[q] = head[q];
         }
         if (nb == 0) {
-          if (fin == 4 || *abort_flag) {
+          if (fin == kGgsEpiWarps || *abort_flag) {
             bool drained = true;
-            for (int q = 0; q < 4; ++q) drained = drained && head[q] == mailbox.tail[q];
+            for (int q = 0; q < kGgsEpiWarps; ++q) drained = drained && head[q] == mailbox.tail[q];
             if (drained) break;
             continue;
           }
@@ -590,21 +663,27 @@ gather_gemm_scatter_kernel(const __grid_constant__ CUtensorMap tma_a, const __gr
       }
     }
   } else {
-    // ---- epilogue (4 warps, 32 accumulator rows each), per tile in two column halves of 128.
-    //  push role: 16-bit partial -> 8 KB half-slab in shared memory -> one bulk copy into the owner's staging slot
-    //  own role : (wait for and add the other ranks' partials) + bias -> output rows
-    const int quarter = warp & 3;
-    uint8_t* buf = epi + quarter * kHalfSlabBytes;
+    // ---- epilogue: 8 warps; warp (quarter, half) owns 32 accumulator rows x 128 columns of every tile and walks
+    //      them in two steps of 64 columns.
+    //  push role: 16-bit partial -> 4 KB staging block -> one bulk copy into the owner's staging slot
+    //  own role : (wait for and add the other ranks' partials) + bias (+ activation) -> staging block -> TMA tile
+    //             store into the output (direct stores when the output's row pitch is not a multiple of 16 bytes)
+    const int ew = warp - 2;
+    const int quarter = warp & 3;            // TMEM lanes [32*quarter, +32): fixed by the hardware per warp
+    const int half = ew >> 2;
+    uint8_t* sbuf = epi + ew * kEpiBlockBytes;
     OutT* out = reinterpret_cast<OutT*>(p.out);
-    const bool vec_ok = (p.ldo % (16 / static_cast<int>(sizeof(OutT)))) == 0;
     int pend = -1;
     int mb_tail = 0;
     int it = 0;
     bool failed = false;
     int owner, li;
     int ntr = 0;
-    const bool tr = quarter == 0 && lane == 0;
-    for (int k = 0; !*abort_flag && !failed && tile_of(k, owner, li); ++k) {
+    const bool tr = ew == 0 && lane == 0;
+    const int r = quarter * 32 + lane;
+    Sched sched{0, 0};
+    int gseq = 0, pend_seq = 0;            // lane 0: bulk groups committed so far; value after the pending push's last
+    while (!*abort_flag && !failed && next_tile(sched, owner, li)) {
       const TileInfo ti = tile_info(p, owner, li, kb_total);
       const int acc = it & 1;
       const uint32_t acc_phase = (it >> 1) & 1;
@@ -613,101 +692,168 @@ gather_gemm_scatter_kernel(const __grid_constant__ CUtensorMap tma_a, const __gr
       if (!mbar_wait(&tfull_bar[acc], acc_phase, abort_flag, p.status, kErrTmemFullTimeout, li)) break;
       if (tr) ggs_trace(p.trace, 1, ntr, 4, li);
       tc_fence_after();
-      const bool mine = !push_role;
-      const InT* stage = reinterpret_cast<const InT*>(p.stage[scat ? p.sme : 0]) + static_cast<size_t>(li) * p.sn * kTileElems;
-      const int r = quarter * 32 + lane;
-#pragma unroll 1
-      for (int h = 0; h < 2; ++h) {
-        if (h * 128 >= ti.cols) break;                         // warp-uniform
-        if (!mine && lane == 0) bulk_wait_group_read_n<0>();   // the previous copy has finished reading `buf`
-        if (mine && scat) {
-          bool ok = true;
-          if (lane < p.sn && lane != p.sme)
-            ok = wait_flag(p.sflags[p.sme] + (static_cast<size_t>(li) * p.sn + lane) * 8 + quarter * 2 + h, p.sepoch,
-                           p.status, li);
-          if (__any_sync(0xffffffffu, !ok)) { failed = true; break; }
-          if (tr) ggs_trace(p.trace, 1, ntr, 5, li * 2 + h);
+      const bool mine = !push_tile;
+      if (mine && scat && sched.ip >= np && pend >= 0) {
+        // no push will follow: the last pushed tile must not wait for a later tile to be announced (its owner
+        // may need it for the very tile this CTA is about to wait on, and vice versa)
+        if (lane == 0) {
+          bulk_wait_group0();
+          mailbox8_put(&mailbox, ew, mb_tail, pend);
         }
-        __syncwarp();
+        pend = -1;
+      }
+      const bool half_live = half * 128 < ti.cols;             // warp-uniform
+      const InT* stage = reinterpret_cast<const InT*>(p.stage[scat ? p.sme : 0]) + static_cast<size_t>(li) * p.sn * kTileElems;
+      if (mine && scat && half_live) {
+        bool ok = true;
+        if (lane < p.sn && lane != p.sme)
+          ok = wait_flag(p.sflags[p.sme] + (static_cast<size_t>(li) * p.sn + lane) * 8 + quarter * 2 + half, p.sepoch,
+                         p.status, li);
+        if (__any_sync(0xffffffffu, !ok)) { failed = true; break; }
+        if (tr) ggs_trace(p.trace, 1, ntr, 5, li);
+      }
+      __syncwarp();
+      const uint32_t t_addr = tmem_base + acc * BN + half * 128 + (static_cast<uint32_t>(quarter * 32) << 16);
 #pragma unroll 1
-        for (int c = 0; c < 4; ++c) {
-          const int c0 = h * 128 + c * 32;
-          if (c0 >= ti.cols) break;
-          uint32_t raw[32];
-          tmem_ld_32x32(tmem_base + acc * BN + c0 + (static_cast<uint32_t>(quarter * 32) << 16), raw);
+      for (int i = 0; i < 2; ++i) {
+        const int cq = half * 2 + i;
+        const int c0 = cq * 64;
+        float v[64];
+        {
+          uint32_t r0[32], r1[32];
+          tmem_ld_32x32(t_addr + i * 64, r0);
+          tmem_ld_32x32(t_addr + i * 64 + 32, r1);
           tmem_wait_ld();
-          float v[32];
 #pragma unroll
-          for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(raw[j]);
-          if (mine) {
-            if (scat) {
-              for (int src = 0; src < p.sn; ++src) {
-                if (src == p.sme) continue;
-                uint4 part[4];
-#pragma unroll
-                for (int q = 0; q < 4; ++q)
-                  part[q] = ld_cg16(stage + static_cast<size_t>(src) * kTileElems + staged_off(r, h * 16 + c * 4 + q));
-#pragma unroll
-                for (int q = 0; q < 4; ++q) {
-                  const InT* hh = reinterpret_cast<const InT*>(&part[q]);
-#pragma unroll
-                  for (int e = 0; e < 8; ++e) v[q * 8 + e] += tof(hh[e]);
-                }
-              }
+          for (int j = 0; j < 32; ++j) { v[j] = __uint_as_float(r0[j]); v[32 + j] = __uint_as_float(r1[j]); }
+        }
+        if (i == 1) {
+          // this warp has read all its columns: the MMA warp may reuse the accumulator
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&tempty_bar[acc]);
+        }
+        const bool live = c0 < ti.cols;                          // warp-uniform
+        if (!mine) {
+          // ---- push: this step's 32 x 64 block of the partial tile goes to its owner (always one bulk group per
+          // step, empty for dead columns, so that "all but the latest two groups" means "the previous tile")
+          if (live) {
+            if (lane == 0) bulk_wait_group_read0();              // the previous copy has finished reading sbuf
+            __syncwarp();
+            stage_row_16bit<InT>(sbuf, lane, v);
+            fence_proxy_async();
+            __syncwarp();
+            if (lane == 0) {
+              InT* dst = reinterpret_cast<InT*>(p.stage[owner]) + (static_cast<size_t>(li) * p.sn + p.sme) * kTileElems;
+              bulk_store(dst + cq * (kBM * 64) + quarter * (32 * 64), sbuf, kEpiBlockBytes);
             }
-            if (p.bias != nullptr) {
+          }
+          if (lane == 0) { bulk_commit_group(); ++gseq; }
+          continue;
+        }
+        if (!live) continue;
+        if (scat) {
+          for (int src = 0; src < p.sn; ++src) {
+            if (src == p.sme) continue;
+            const InT* part = stage + static_cast<size_t>(src) * kTileElems;
+            uint4 pc[8];
 #pragma unroll
-              for (int j = 0; j < 32; ++j)
-                if (c0 + j < ti.cols) v[j] += __ldg(p.bias + ti.ocol + c0 + j);
-            }
-            if (r < ti.rows) {
-              const size_t o = static_cast<size_t>(ti.orow + r) * p.ldo + ti.ocol + c0;
-              if (p.z_out != nullptr)
-                store_row<InT>(reinterpret_cast<InT*>(p.z_out) + o, v, (p.ldo % 8 == 0) && c0 + 32 <= ti.cols, ti.cols - c0);
-              if (p.act == kActGelu) {
+            for (int j = 0; j < 8; ++j) pc[j] = ld_cg16(part + staged_off_v2(r, cq, j));
 #pragma unroll
-                for (int j = 0; j < 32; ++j) v[j] = gelu_fast(v[j]);
-              } else if (p.act == kActRelu) {
+            for (int j = 0; j < 8; ++j) {
+              const InT* hh = reinterpret_cast<const InT*>(&pc[j]);
 #pragma unroll
-                for (int j = 0; j < 32; ++j) v[j] = fmaxf(v[j], 0.f);
-              }
-              store_row(out + o, v, vec_ok && c0 + 32 <= ti.cols, ti.cols - c0);
-            }
-          } else {
-#pragma unroll
-            for (int q = 0; q < 4; ++q) {
-              uint4 u;
-              u.x = pack2(v[q * 8 + 0], v[q * 8 + 1], InT());
-              u.y = pack2(v[q * 8 + 2], v[q * 8 + 3], InT());
-              u.z = pack2(v[q * 8 + 4], v[q * 8 + 5], InT());
-              u.w = pack2(v[q * 8 + 6], v[q * 8 + 7], InT());
-              *reinterpret_cast<uint4*>(buf + (lane * 128 + (((c * 4 + q) ^ (lane & 15)) << 3)) * 2) = u;
+              for (int e = 0; e < 8; ++e) v[j * 8 + e] += tof(hh[e]);
             }
           }
         }
-        if (!mine) {
-          fence_proxy_async();
-          __syncwarp();
-          if (lane == 0) {
-            InT* dst = reinterpret_cast<InT*>(p.stage[owner]) + (static_cast<size_t>(li) * p.sn + p.sme) * kTileElems;
-            bulk_store(dst + h * (kBM * 128) + quarter * 32 * 128, buf, kHalfSlabBytes);
-            bulk_commit_group();
-            bulk_wait_group_1();                               // everything but the copy just issued has completed
-            if (pend >= 0) mailbox_put(&mailbox, quarter, mb_tail, 0, pend);
-            pend = ((li * p.sn + owner) << 3) | (quarter << 1) | h;
+        if (p.bias != nullptr) {
+#pragma unroll
+          for (int j = 0; j < 64; ++j) v[j] += (c0 + j < ti.cols) ? __ldg(p.bias + ti.ocol + c0 + j) : 0.f;
+        }
+        const int gx = ti.ocol + c0, gy = ti.orow + quarter * 32;
+        if (p.tma_store) {
+          if (p.z_out != nullptr) {
+            if (lane == 0) bulk_wait_group_read0();
+            __syncwarp();
+            stage_row_16bit<InT>(sbuf, lane, v);
+            fence_proxy_async();
+            __syncwarp();
+            if (lane == 0) { tma_store_2d(&tma_z, sbuf, gx, gy); bulk_commit_group(); ++gseq; }
+          }
+          if (p.act == kActGelu) {
+#pragma unroll
+            for (int j = 0; j < 64; ++j) v[j] = gelu_fast(v[j]);
+          } else if (p.act == kActRelu) {
+#pragma unroll
+            for (int j = 0; j < 64; ++j) v[j] = fmaxf(v[j], 0.f);
+          }
+          if constexpr (OUT_F32) {
+#pragma unroll
+            for (int hh = 0; hh < 2; ++hh) {
+              if (c0 + hh * 32 >= ti.cols) break;
+              float w32[32];
+#pragma unroll
+              for (int j = 0; j < 32; ++j) w32[j] = v[hh * 32 + j];
+              if (lane == 0) bulk_wait_group_read0();
+              __syncwarp();
+              stage_row_f32(sbuf, lane, w32);
+              fence_proxy_async();
+              __syncwarp();
+              if (lane == 0) { tma_store_2d(&tma_out, sbuf, gx + hh * 32, gy); bulk_commit_group(); ++gseq; }
+            }
+          } else {
+            if (lane == 0) bulk_wait_group_read0();
+            __syncwarp();
+            stage_row_16bit<InT>(sbuf, lane, v);
+            fence_proxy_async();
+            __syncwarp();
+            if (lane == 0) { tma_store_2d(&tma_out, sbuf, gx, gy); bulk_commit_group(); ++gseq; }
+          }
+        } else if (r < ti.rows) {
+          const size_t o = static_cast<size_t>(ti.orow + r) * p.ldo + gx;
+#pragma unroll
+          for (int hh = 0; hh < 2; ++hh) {
+            if (c0 + hh * 32 >= ti.cols) break;
+            float w32[32];
+#pragma unroll
+            for (int j = 0; j < 32; ++j) w32[j] = v[hh * 32 + j];
+            if (p.z_out != nullptr)
+              store_row<InT>(reinterpret_cast<InT*>(p.z_out) + o + hh * 32, w32, false, ti.cols - c0 - hh * 32);
+            if (p.act == kActGelu) {
+#pragma unroll
+              for (int j = 0; j < 32; ++j) w32[j] = gelu_fast(w32[j]);
+            } else if (p.act == kActRelu) {
+#pragma unroll
+              for (int j = 0; j < 32; ++j) w32[j] = fmaxf(w32[j], 0.f);
+            }
+            store_row(out + o + hh * 32, w32, false, ti.cols - c0 - hh * 32);
           }
         }
       }
-      if (failed) break;
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&tempty_bar[acc]);
+      if (lane == 0) {
+        // a pushed tile is announced once its copies have landed, which is known without draining the pipeline as
+        // soon as this warp has committed two more groups: "all but the latest two have completed"
+        if (pend >= 0 && gseq - pend_seq >= 2) {
+          bulk_wait_group_n<2>();
+          mailbox8_put(&mailbox, ew, mb_tail, pend);
+          pend = -1;
+        }
+        if (!mine) {
+          if (pend >= 0) {                 // (only when a tile committed fewer than two groups in between)
+            bulk_wait_group_n<2>();
+            mailbox8_put(&mailbox, ew, mb_tail, pend);
+          }
+          pend = half_live ? (((li * p.sn + owner) << 3) | (quarter << 1) | half) : -1;
+          pend_seq = gseq;
+        }
+      }
       if (tr) ggs_trace(p.trace, 1, ntr, 6, li);
     }
     if (failed) *abort_flag = 1;
     if (lane == 0) {
       bulk_wait_group0();
-      if (pend >= 0) mailbox_put(&mailbox, quarter, mb_tail, 0, pend);
+      if (pend >= 0) mailbox8_put(&mailbox, ew, mb_tail, pend);
       __threadfence_block();
       atomicAdd(const_cast<int*>(&mailbox.finished), 1);
     }
@@ -730,24 +876,25 @@ gather_gemm_scatter_kernel(const __grid_constant__ CUtensorMap tma_a, const __gr
 
 template <bool AK, bool BK_, typename InT, bool F32>
 static void launch_ggs(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tao, const CUtensorMap& tbo,
-                       const GgsParams& p, cudaStream_t stream) {
+                       const CUtensorMap& to, const CUtensorMap& tz, const GgsParams& p, cudaStream_t stream) {
   auto kern = gather_gemm_scatter_kernel<AK, BK_, InT, F32>;
   static bool configured = false;
   if (!configured) {
-    C10_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kFusedSmemBytes));
+    C10_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kGgsSmemBytes));
     configured = true;
   }
-  kern<<<p.num_gemm_ctas + p.num_comm_ctas, kFusedThreads, kFusedSmemBytes, stream>>>(ta, tb, tao, tbo, p);
+  kern<<<p.num_gemm_ctas + p.num_comm_ctas, kGgsThreads, kGgsSmemBytes, stream>>>(ta, tb, tao, tbo, to, tz, p);
   C10_CUDA_KERNEL_LAUNCH_CHECK();
 }
 
 template <typename InT, bool F32>
 static void dispatch_ggs(bool ak, bool bk, const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tao,
-                         const CUtensorMap& tbo, const GgsParams& p, cudaStream_t stream) {
-  if (ak && bk) launch_ggs<true, true, InT, F32>(ta, tb, tao, tbo, p, stream);
-  else if (ak && !bk) launch_ggs<true, false, InT, F32>(ta, tb, tao, tbo, p, stream);
-  else if (!ak && bk) launch_ggs<false, true, InT, F32>(ta, tb, tao, tbo, p, stream);
-  else launch_ggs<false, false, InT, F32>(ta, tb, tao, tbo, p, stream);
+                         const CUtensorMap& tbo, const CUtensorMap& to, const CUtensorMap& tz, const GgsParams& p,
+                         cudaStream_t stream) {
+  if (ak && bk) launch_ggs<true, true, InT, F32>(ta, tb, tao, tbo, to, tz, p, stream);
+  else if (ak && !bk) launch_ggs<true, false, InT, F32>(ta, tb, tao, tbo, to, tz, p, stream);
+  else if (!ak && bk) launch_ggs<false, true, InT, F32>(ta, tb, tao, tbo, to, tz, p, stream);
+  else launch_ggs<false, false, InT, F32>(ta, tb, tao, tbo, to, tz, p, stream);
 }
 
 // One operand's gather, as the host describes it: cfg = [] (not gathered) or [n, me, g, panel_rows, epoch];
@@ -904,13 +1051,23 @@ static void gather_gemm_scatter(torch::Tensor a, torch::Tensor b, bool trans_a, 
   CUtensorMap tb = make_tma_2d(b_ptr, br, b.size(1), b.size(1), bk ? kFusedBN : 64);
   CUtensorMap tao = make_tma_2d(a.data_ptr(), a.size(0), a.size(1), a.size(1), ak ? kBM : 64);
   CUtensorMap tbo = make_tma_2d(b.data_ptr(), b.size(0), b.size(1), b.size(1), bk ? kFusedBN : 64);
+  // tile stores through TMA need a 16-byte aligned base and row pitch; anything else takes the direct-store path
+  const int out_bytes = f32 ? 4 : 2;
+  const bool out_ok = (reinterpret_cast<uintptr_t>(p.out) & 15) == 0 && (static_cast<size_t>(p.ldo) * out_bytes) % 16 == 0;
+  const bool z_ok = p.z_out == nullptr || ((reinterpret_cast<uintptr_t>(p.z_out) & 15) == 0 && (static_cast<size_t>(p.ldo) * 2) % 16 == 0);
+  p.tma_store = (out_ok && z_ok) ? 1 : 0;
+  CUtensorMap to = tao, tz = tao;     // placeholders when unused
+  if (p.tma_store) {
+    to = make_tma_2d_store(p.out, p.Ms, p.Ns, p.ldo, out_bytes, p.is_bf16);
+    if (p.z_out != nullptr) tz = make_tma_2d_store(p.z_out, p.Ms, p.Ns, p.ldo, 2, p.is_bf16);
+  }
   auto stream = at::cuda::getCurrentCUDAStream();
   if (p.is_bf16) {
-    if (f32) dispatch_ggs<__nv_bfloat16, true>(ak, bk, ta, tb, tao, tbo, p, stream);
-    else dispatch_ggs<__nv_bfloat16, false>(ak, bk, ta, tb, tao, tbo, p, stream);
+    if (f32) dispatch_ggs<__nv_bfloat16, true>(ak, bk, ta, tb, tao, tbo, to, tz, p, stream);
+    else dispatch_ggs<__nv_bfloat16, false>(ak, bk, ta, tb, tao, tbo, to, tz, p, stream);
   } else {
-    if (f32) dispatch_ggs<__half, true>(ak, bk, ta, tb, tao, tbo, p, stream);
-    else dispatch_ggs<__half, false>(ak, bk, ta, tb, tao, tbo, p, stream);
+    if (f32) dispatch_ggs<__half, true>(ak, bk, ta, tb, tao, tbo, to, tz, p, stream);
+    else dispatch_ggs<__half, false>(ak, bk, ta, tb, tao, tbo, to, tz, p, stream);
   }
 }
 

@@ -132,7 +132,7 @@ def fused_gemm_all_reduce(a, b, trans_a, trans_b, mode, bias, out_dtype):
 
 _GATHER_HALF = int(os.environ.get("CUBEWORK_B200_GATHER_MB", "384")) << 20      # per operand role and half
 _RS_HALF = int(os.environ.get("CUBEWORK_B200_RS_STAGE_MB", "384")) << 20        # staging of partial tiles, per half
-_PUSH_CTAS = int(os.environ.get("CUBEWORK_B200_PUSH_CTAS", "16"))
+_PUSH_CTAS = int(os.environ.get("CUBEWORK_B200_PUSH_CTAS", "0"))     # 0: chosen per call by _push_ctas
 _MAX_PANELS = 2048                                                              # (source, panel) flags per operand
 _LOWP = (torch.bfloat16, torch.float16)
 
@@ -155,6 +155,18 @@ def _plan_gather(t, spec, mn_major):
     while n * ((R + panel_rows - 1) // panel_rows) > _MAX_PANELS:
         panel_rows *= 2
     return n, g, panel_rows
+
+
+def _push_ctas(push_bytes, M, N, K, n):
+    """Communication CTAs for the operand gathers of one call.  One CTA moves about 40 GB/s (32 KB pieces, a dozen
+    in flight).  The GEMM CTAs start with the tiles that need no remote data (1/n of the work) and then follow
+    the arrival order, so the shards should be out within the remaining (n-1)/n of the product's time; more than
+    the links carry (about 750 GB/s) is pointless, and every communication CTA is an SM the GEMM loses."""
+    if _PUSH_CTAS > 0:
+        return _PUSH_CTAS
+    t_gemm = max(2.0 * M * N * K / 1.2e15, 20e-6)
+    rate = min(push_bytes / (0.8 * t_gemm * (n - 1) / n), 750e9)
+    return int(min(20, max(4, -(-rate // 40e9))))
 
 
 def _aligned(t):
@@ -242,10 +254,12 @@ def fused_gather_gemm_scatter(a, b, trans_a, trans_b, gather_a, gather_b, scatte
         sc_cfg = [sc[1], sc[2], ws.me, ws.epoch]
     out = torch.empty((Ms, Ns), dtype=out_dtype, device=a.device)
     z = torch.empty((Ms, Ns), dtype=a.dtype, device=a.device) if pre_act_out else None
+    push_bytes = sum((plan[0] - 1) * t.numel() * t.element_size() for plan, t in ((ga, a), (gb, b)) if plan is not None)
+    comm_ctas = _push_ctas(push_bytes, M, N, K, max(plan[0] for plan in (ga, gb) if plan is not None) if (ga or gb) else 1)
     ext._count(1)
     STATS["gather_gemm_scatter"] += 1
     m.gather_gemm_scatter(a, b, bool(trans_a), bool(trans_b), bias, out, ga_cfg, ga_bufs, ga_flags, gb_cfg, gb_bufs,
-                          gb_flags, sc_cfg, sc_stage, sc_flags, _PUSH_CTAS, m.status_device_ptr(), _ACT_CODE[act], z,
+                          gb_flags, sc_cfg, sc_stage, sc_flags, comm_ctas, m.status_device_ptr(), _ACT_CODE[act], z,
                           GGS_TRACE)
     from . import collective
     if collective._profiler is not None:
