@@ -22,13 +22,19 @@ VOCAB = 50304
 def build(args):
     kw = {} if args.dropout is None else dict(dropout=args.dropout, embedding_dropout=args.dropout)
     model = gpt2.build_model(args.model_name, max_position_embeddings=args.seq_length,
-                             checkpoint=args.use_activation_checkpoint, **kw)
+                             checkpoint=args.use_activation_checkpoint, init_std=0.02, **kw)
 
     def make_batch(g, micro):
         ids = torch.randint(0, VOCAB if args.model_name != "gpt2_tiny" else 1024, (micro, args.seq_length), generator=g)
         return dict(input_ids=ids, attention_mask=torch.ones(micro, args.seq_length), labels=ids.clone())
 
     return model, gpt2.GPT2LMLoss(), cube_nn.Perplexity(), make_batch, args.seq_length
+
+
+def build_data(args, micro, model):
+    from cubework_b200.utils.datasets import language_model_loaders
+    return language_model_loaders(args.dataset_path, args.tokenizer_path, args.seq_length, micro,
+                                  num_workers=args.num_workers)
 
 
 def forward(model, batch):

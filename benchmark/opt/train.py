@@ -23,8 +23,10 @@ SCHEDULE = "linear"
 
 def build(args):
     kw = {} if args.dropout is None else dict(dropout=args.dropout)
+    if getattr(args, "pure_16bit", False):      # -O3: parameters (and gradients, optimizer updates) in the AMP dtype
+        kw["dtype"] = torch.bfloat16 if args.amp_dtype == "bf16" else torch.float16
     model = opt.build_model(args.model_name, max_position_embeddings=args.seq_length,
-                            checkpoint=args.use_activation_checkpoint, **kw)
+                            checkpoint=args.use_activation_checkpoint, init_std=0.02, **kw)
     vocab = model.vocab_size
 
     def make_batch(g, micro):
@@ -34,12 +36,20 @@ def build(args):
     return model, opt.OPTLMLoss(), cube_nn.Perplexity(), make_batch, args.seq_length
 
 
+def build_data(args, micro, model):
+    from cubework_b200.utils.datasets import language_model_loaders
+    return language_model_loaders(args.dataset_path, args.tokenizer_path, args.seq_length, micro,
+                                  num_workers=args.num_workers)
+
+
 def forward(model, batch):
     return model(batch["input_ids"], batch["attention_mask"])[0], batch["labels"]
 
 
 if __name__ == "__main__":
     parser = driver.get_parser("OPT on cubework_b200", "opt_125m")
+    parser.add_argument("-O3", dest="pure_16bit", action="store_true",
+                        help="keep the parameters themselves in the AMP dtype (no fp32 master copies)")
     args = cube.initialize_distributed(parser)
     driver.run(args, sys.modules[__name__])
     cube.destroy_distributed()

@@ -28,7 +28,12 @@ def build(args):
         return dict(pixel_values=torch.randn(micro, 3, img, img, generator=g),
                     labels=torch.randint(0, classes, (micro, ), generator=g))
 
-    return model, vit.MixupLoss(), vit.MixupAccuracy(), make_batch, 1
+    return model, vit.MixupLoss(), vit.MixupAccuracy(), make_batch, 1    # one "token" per image: throughput in images
+
+
+def build_data(args, micro, model):
+    from cubework_b200.utils.datasets import cifar10_loaders
+    return cifar10_loaders(args.dataset_path, model.img_size, micro, num_workers=args.num_workers)
 
 
 def forward(model, batch):

@@ -19,15 +19,19 @@ from .utils.clip_grad import clip_grad_norm
 class Trainer:
 
     def __init__(self, model, criterion, optimizer, lr_scheduler=None, *, amp_dtype=torch.bfloat16, clip=None,
-                 accum_steps=1, forward_fn=None, device=None):
+                 accum_steps=1, forward_fn=None, device=None, scaler_kwargs=None, timer=None):
         """``forward_fn(model, batch) -> (outputs, targets)``; default feeds ``batch`` as kwargs minus
-        ``labels`` and uses ``batch["labels"]`` as targets."""
+        ``labels`` and uses ``batch["labels"]`` as targets.  ``scaler_kwargs`` (``init_scale``, ``growth_factor``,
+        ``backoff_factor``, ``growth_interval``) configure the loss scaler of fp16 runs (benchmark/gpt2/train.py:
+        316-319, 340-347 in the reference).  ``timer`` (an object with ``start(name)`` / ``stop(name)``) receives
+        the phases ``data``, ``fwd``, ``bwd`` and ``opt`` of every step (train.py:79-129)."""
         self.model, self.criterion, self.optimizer, self.lr_scheduler = model, criterion, optimizer, lr_scheduler
         self.amp_dtype, self.clip, self.accum_steps = amp_dtype, clip, accum_steps
         self.forward_fn = forward_fn or self._default_forward
         self.device = device or next(model.parameters()).device
-        self.scaler = torch.amp.GradScaler("cuda") if (amp_dtype == torch.float16 and self.device.type == "cuda") \
-            else None
+        self.scaler = torch.amp.GradScaler("cuda", **(scaler_kwargs or {})) \
+            if (amp_dtype == torch.float16 and self.device.type == "cuda") else None
+        self.timer = timer
         self._copy_stream = torch.cuda.Stream() if self.device.type == "cuda" else None
         self.h2d_bytes = 0
         self.steps = 0
@@ -47,18 +51,22 @@ class Trainer:
         """Asynchronous host->device copy of a dict of (pinned) host tensors."""
         if self.device.type != "cuda":
             return batch
-        out = {}
+        moved = []
+
+        def move(v):
+            if torch.is_tensor(v) and v.device.type == "cpu":
+                self.h2d_bytes += v.numel() * v.element_size()
+                v = v.to(self.device, non_blocking=True)
+                moved.append(v)
+            elif isinstance(v, (tuple, list)):       # e.g. mixed-up labels: (labels, permuted labels, lambda)
+                v = type(v)(move(x) for x in v)
+            return v
+
         with torch.cuda.stream(self._copy_stream):
-            for k, v in batch.items():
-                if torch.is_tensor(v) and v.device.type == "cpu":
-                    self.h2d_bytes += v.numel() * v.element_size()
-                    out[k] = v.to(self.device, non_blocking=True)
-                else:
-                    out[k] = v
+            out = {k: move(v) for k, v in batch.items()}
         torch.cuda.current_stream().wait_stream(self._copy_stream)
-        for v in out.values():
-            if torch.is_tensor(v):
-                v.record_stream(torch.cuda.current_stream())
+        for v in moved:
+            v.record_stream(torch.cuda.current_stream())
         return out
 
     def _autocast(self):
@@ -74,21 +82,35 @@ class Trainer:
             self.model.train()
         total = None
         n = len(batches)
+        tm = self.timer
         for i, batch in enumerate(batches):
+            if tm is not None:
+                tm.start("data")
             batch = self.to_device(batch)
+            if tm is not None:
+                tm.stop("data")
             sync_ctx = contextlib.nullcontext()
             if i < n - 1 and hasattr(self.model, "no_sync"):
                 sync_ctx = self.model.no_sync()
             with sync_ctx:
+                if tm is not None:
+                    tm.start("fwd")
                 with self._autocast():
                     out, targets = self.forward_fn(self.model, batch)
                     loss = self.criterion(out, targets)
+                if tm is not None:
+                    tm.stop("fwd")
+                    tm.start("bwd")
                 scaled = loss / n if n > 1 else loss
                 if self.scaler is not None:
                     self.scaler.scale(scaled).backward()
                 else:
                     scaled.backward()
+                if tm is not None:
+                    tm.stop("bwd")
             total = loss.detach() if total is None else total + loss.detach()
+        if tm is not None:
+            tm.start("opt")
         _sync_async_grads()
         if self._partial_params:
             reduce_partial_grads(self._partial_params)
@@ -104,6 +126,8 @@ class Trainer:
         if self.lr_scheduler is not None:
             self.lr_scheduler.step()
         self.optimizer.zero_grad(set_to_none=True)
+        if tm is not None:
+            tm.stop("opt")
         self.steps += 1
         if self.device.type == "cuda" and self.steps % self.status_interval == 0:
             self.check_device_status()

@@ -19,7 +19,26 @@ from .utils.common import set_device, set_seed
 from .utils.logging import get_logger, init_logger
 
 _DEFAULT_SEED = 1024
-__version__ = "0.1.0"
+
+
+def _get_version():
+    """``version.txt`` of a checkout, the installed distribution's version otherwise (reference: initialize.py:13-21
+    reads ``version.txt`` and falls back to 0.0.0)."""
+    import os
+    path = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "version.txt")
+    try:
+        with open(path) as f:
+            return f.read().strip() or "0.0.0"
+    except OSError:
+        pass
+    try:
+        from importlib.metadata import version
+        return version("cubework_b200")
+    except Exception:  # noqa: BLE001
+        return "0.0.0"
+
+
+__version__ = _get_version()
 
 
 def initialize_distributed(parser=None, argv=None, timeout_s: float = 1800.0):

@@ -17,6 +17,11 @@ class SelfAttention(nn.Module):
     (benchmark/gpt2/gpt2.py:66-96, vit/vit.py:74-89, opt/opt.py:70-128), so any contiguous shard of
     its output features holds whole heads and the local head count follows from the local width.
     Scores never reach HBM: the attention itself is one flash-style kernel.
+
+    Dropout on the attention probabilities (``attention_dropout``; reference gpt2.py:62,84-86, vit.py:63,84,
+    opt.py:141) is applied in training mode by the materialised formulation of the reference - scores, softmax,
+    :class:`cubework_b200.module.Dropout` (per-rank TENSOR stream in 2D / 3D), product with V - because the fused
+    kernel has no random-number path; with ``attention_dropout == 0`` or in evaluation mode the fused kernel runs.
     """
 
     def __init__(self, hidden_size, num_heads, attention_dropout=0.0, dropout=0.0, bias=True, causal=False,
@@ -29,14 +34,18 @@ class SelfAttention(nn.Module):
         self.attention_dropout_p = attention_dropout
         self.dense = cube_nn.Linear(hidden_size, hidden_size, bias=out_bias, **sp, **(out_kw or {}))
         self.dropout = cube_nn.Dropout(dropout, **sp)
-        if attention_dropout:
-            raise NotImplementedError("dropout on attention probabilities is not supported by the fused kernel")
+        # heads are sharded in every mode, so the probabilities differ per rank: per-rank random stream
+        self.attention_dropout = cube_nn.Dropout(attention_dropout, sequence_parallel=True)
 
     def forward(self, x, key_bias=None):
         qkv = self.query_key_value(x)
         b, t, w = qkv.shape
         heads = w // (3 * self.head_dim)
-        ctx = ops.attention_packed(qkv.view(b, t, heads, 3 * self.head_dim), self.causal, key_bias)
+        qkv = qkv.view(b, t, heads, 3 * self.head_dim)
+        if self.attention_dropout_p > 0.0 and self.training:
+            ctx = ops.attention_with_prob_dropout(qkv, self.causal, key_bias, self.attention_dropout)
+        else:
+            ctx = ops.attention_packed(qkv, self.causal, key_bias)
         return self.dropout(self.dense(ctx))
 
 

@@ -13,16 +13,20 @@ import torch.nn as nn
 from .. import module as cube_nn
 from .. import ops
 from ..parallel.loss import IGNORE_INDEX
-from .common import MLP, SelfAttention, key_bias_from_mask, maybe_checkpoint
+from .common import MLP, SelfAttention, key_bias_from_mask, maybe_checkpoint, normal_init
+
+
+def _init_kw(init_std):
+    return {} if init_std is None else dict(weight_initializer=normal_init(init_std))
 
 
 class OPTLearnedPositionalEmbedding(nn.Module):
     """Positions = (cumulative count of real tokens) - 1, shifted by 2 into a ``[max_pos + 2, H]`` table."""
 
-    def __init__(self, num_embeddings, embedding_dim, dtype=None):
+    def __init__(self, num_embeddings, embedding_dim, dtype=None, init_std=None):
         super().__init__()
         self.offset = 2
-        self.embed = cube_nn.Embedding(num_embeddings + self.offset, embedding_dim, dtype=dtype)
+        self.embed = cube_nn.Embedding(num_embeddings + self.offset, embedding_dim, dtype=dtype, **_init_kw(init_std))
 
     def forward(self, attention_mask, past_key_values_length=0):
         m = attention_mask.long()
@@ -34,8 +38,8 @@ class OPTLearnedPositionalEmbedding(nn.Module):
 
 class OPTAttention(SelfAttention):
 
-    def __init__(self, embed_dim, num_heads, dropout=0.0, bias=True, dtype=None):
-        kw = dict(dtype=dtype)
+    def __init__(self, embed_dim, num_heads, dropout=0.0, bias=True, dtype=None, init_std=None):
+        kw = dict(dtype=dtype, **_init_kw(init_std))
         super().__init__(embed_dim, num_heads, attention_dropout=dropout, dropout=0.0, bias=bias, causal=True,
                          qkv_kw=kw, out_kw=kw, out_bias=bias)
 
@@ -56,14 +60,16 @@ class OPTAttention(SelfAttention):
 class OPTDecoderLayer(nn.Module):
 
     def __init__(self, hidden_size=768, ffn_dim=3072, num_attention_heads=12, attention_dropout=0.0, dropout=0.1,
-                 do_layer_norm_before=True, activation_function="relu", gradient_checkpointing=False, dtype=None):
+                 do_layer_norm_before=True, activation_function="relu", gradient_checkpointing=False, dtype=None,
+                 init_std=None):
         super().__init__()
         self.do_layer_norm_before = do_layer_norm_before
         self.gradient_checkpointing = gradient_checkpointing
-        self.self_attn = OPTAttention(hidden_size, num_attention_heads, attention_dropout, dtype=dtype)
+        self.self_attn = OPTAttention(hidden_size, num_attention_heads, attention_dropout, dtype=dtype,
+                                      init_std=init_std)
         self.dropout = cube_nn.Dropout(dropout)
         self.self_attn_layer_norm = cube_nn.LayerNorm(hidden_size, dtype=dtype)
-        kw = dict(dtype=dtype)
+        kw = dict(dtype=dtype, **_init_kw(init_std))
         self.ffn = MLP(hidden_size, ffn_dim, activation_function, dropout, kw1=kw, kw2=kw)
         self.final_layer_norm = cube_nn.LayerNorm(hidden_size, dtype=dtype)
 
@@ -114,16 +120,21 @@ class OPT(nn.Module):
 
     def __init__(self, vocab_size=50304, hidden_size=768, num_hidden_layers=12, ffn_dim=3072, num_attention_heads=12,
                  max_position_embeddings=1024, do_layer_norm_before=True, dropout=0.1, attention_dropout=0.0,
-                 layerdrop=0.0, padding_idx=1, activation_function="relu", gradient_checkpointing=False, dtype=None):
+                 layerdrop=0.0, padding_idx=1, activation_function="relu", gradient_checkpointing=False, dtype=None,
+                 init_std=None):
+        """``init_std``: every weight matrix and embedding table is drawn from N(0, init_std) (the HF OPT recipe uses
+        0.02; ``None`` keeps the layers' own defaults).  ``dtype``: parameter dtype; a 16-bit dtype gives the pure
+        16-bit-parameter mode of the reference's ``-O3`` (benchmark/opt/opt.py:541), without fp32 master copies."""
         super().__init__()
         self.layerdrop, self.padding_idx, self.vocab_size = layerdrop, padding_idx, vocab_size
         self.max_target_positions = max_position_embeddings
         self.embed_tokens = cube_nn.Embedding(vocab_size, hidden_size, vocab_parallel=True, padding_idx=padding_idx,
-                                              dtype=dtype)
-        self.embed_positions = OPTLearnedPositionalEmbedding(max_position_embeddings, hidden_size, dtype=dtype)
+                                              dtype=dtype, **_init_kw(init_std))
+        self.embed_positions = OPTLearnedPositionalEmbedding(max_position_embeddings, hidden_size, dtype=dtype,
+                                                             init_std=init_std)
         self.layers = nn.ModuleList([
             OPTDecoderLayer(hidden_size, ffn_dim, num_attention_heads, attention_dropout, dropout,
-                            do_layer_norm_before, activation_function, gradient_checkpointing, dtype)
+                            do_layer_norm_before, activation_function, gradient_checkpointing, dtype, init_std)
             for _ in range(num_hidden_layers)
         ])
         self.final_layer_norm = cube_nn.LayerNorm(hidden_size, dtype=dtype) if do_layer_norm_before else None

@@ -80,6 +80,7 @@ class VisionTransformer(nn.Module):
         self.img_size, self.patch_size = img_size, patch_size
         self.embed = ViTEmbedding(img_size, patch_size, in_chans, hidden_size, dropout)
         self.num_patches = self.embed.patch_embed.embed.num_patches
+        self.flop_tokens_per_sample = self.num_patches + 1      # what the FLOP model counts per image (patches + class token)
         dpr = [x.item() for x in torch.linspace(0, drop_path, depth)]
         self.blocks = nn.ModuleList([
             ViTBlock(hidden_size, num_heads, intermediate_size, attention_dropout, dropout, dpr[i], layernorm_epsilon,

@@ -314,6 +314,25 @@ def attention_packed(qkv: torch.Tensor, causal: bool, key_bias: Optional[torch.T
     return o.transpose(1, 2).reshape(B, T, H * dh)
 
 
+def attention_with_prob_dropout(qkv: torch.Tensor, causal: bool, key_bias: Optional[torch.Tensor], dropout,
+                                scale: Optional[float] = None) -> torch.Tensor:
+    """Self-attention with ``dropout`` (a module) applied to the probabilities: the materialised formulation
+    ``softmax(QK^T * scale + mask) -> dropout -> @ V`` on packed QKV ``[B, T, heads, 3*dh]`` (autograd by PyTorch).
+    The softmax runs in fp32; the two batched products run in the tensor's dtype."""
+    B, T, H, D3 = qkv.shape
+    dh = D3 // 3
+    scale = scale if scale is not None else 1.0 / math.sqrt(dh)
+    q, k, v = qkv.permute(0, 2, 1, 3).chunk(3, dim=-1)
+    s = torch.matmul(q, k.transpose(-1, -2)).float() * scale
+    if causal:
+        keep = torch.ones(T, T, dtype=torch.bool, device=s.device).tril()
+        s = s.masked_fill(~keep, float("-inf"))
+    if key_bias is not None:
+        s = s + key_bias.float()[:, None, None, :]
+    p = dropout(torch.softmax(s, dim=-1).to(qkv.dtype))
+    return torch.matmul(p, v).transpose(1, 2).reshape(B, T, H * dh)
+
+
 # ---------------------------------------------------------------------------------------------------
 # embedding
 # ---------------------------------------------------------------------------------------------------

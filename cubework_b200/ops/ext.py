@@ -79,51 +79,67 @@ def check_status(clear=True):
 
 
 # --------------------------------------------------------------------------------------------------------
-def _gemm_ok(a, b, trans_a, trans_b):
-    """TMA needs 16-byte aligned bases and leading dimensions that are multiples of 8 elements."""
-    return (a.shape[1] % 8 == 0 and b.shape[1] % 8 == 0 and a.data_ptr() % 16 == 0 and b.data_ptr() % 16 == 0)
+# TMA reads need 16-byte aligned bases and row pitches: operands whose last dimension is not a multiple of eight
+# 16-bit elements are zero-padded (a copy) rather than handed to a library GEMM; the result is cut back.
+def _pad_cols(t, mult=8):
+    extra = (-t.shape[1]) % mult
+    return torch.nn.functional.pad(t, (0, extra)) if extra else t
+
+
+def _pad_rows(t, rows):
+    return torch.nn.functional.pad(t, (0, 0, 0, rows - t.shape[0])) if rows != t.shape[0] else t
+
+
+def _tma_ready(t):
+    t = t.contiguous()
+    return t if t.data_ptr() % 16 == 0 else t.clone()
 
 
 def gemm(a, b, trans_a, trans_b, bias, act, out_dtype, pre_act_out):
-    a = a.contiguous()
-    b = b.contiguous()
     out_f32 = out_dtype == torch.float32
-    if not _gemm_ok(a, b, trans_a, trans_b) or (not out_f32 and out_dtype != a.dtype):
-        _warn_once(("gemm", tuple(a.shape), tuple(b.shape)),
-                   f"GEMM operands {tuple(a.shape)} x {tuple(b.shape)} are not TMA-compatible; using torch.matmul")
-        A = a.t() if trans_a else a
-        B = b.t() if trans_b else b
-        z = A @ B
-        if bias is not None:
-            z = z + bias.to(z.dtype)
-        y = torch.nn.functional.gelu(z) if act == "gelu" else torch.relu(z) if act == "relu" else z
-        return (y.to(out_dtype), z.to(out_dtype)) if pre_act_out else y.to(out_dtype)
+    if not out_f32 and out_dtype != a.dtype:
+        raise ValueError(f"GEMM output dtype must be float32 or the operands' dtype ({a.dtype}), got {out_dtype}")
+    M = a.shape[1] if trans_a else a.shape[0]
+    N = b.shape[0] if trans_b else b.shape[1]
+    if a.shape[1] % 8 or b.shape[1] % 8:
+        a, b = _pad_cols(a), _pad_cols(b)           # pads K (K-major operand) or M / N (MN-major operand) with zeros
+        ka = a.shape[0] if trans_a else a.shape[1]
+        kb = b.shape[1] if trans_b else b.shape[0]
+        k = max(ka, kb)                             # the other operand follows a padded K with zero rows / columns
+        if ka != k:
+            a = _pad_rows(a, k) if trans_a else torch.nn.functional.pad(a, (0, k - ka))
+        if kb != k:
+            b = torch.nn.functional.pad(b, (0, k - kb)) if trans_b else _pad_rows(b, k)
+        n_pad = b.shape[0] if trans_b else b.shape[1]
+        if bias is not None and n_pad != N:
+            bias = torch.nn.functional.pad(bias, (0, n_pad - N))
+    a, b = _tma_ready(a), _tma_ready(b)
     _count(1)
     out, z = require().gemm(a, b, bool(trans_a), bool(trans_b), bias, act or "", out_f32, bool(pre_act_out))
+    if out.shape[0] != M or out.shape[1] != N:
+        out = out[:M, :N].contiguous()
+        z = z[:M, :N].contiguous() if pre_act_out else z
     return (out, z) if pre_act_out else out
 
 
 def act_backward(dy, z, act, want_bias_grad):
     code = {"gelu": 1, "relu": 2}[act]
-    if dy.shape[1] % 8 != 0:
-        zf = z.float()
-        if act == "gelu":
-            dz = dy.float() * (0.5 * (1 + torch.erf(zf * 0.7071067811865476)) +
-                               zf * torch.exp(-0.5 * zf * zf) * 0.3989422804014327)
-        else:
-            dz = dy.float() * (zf > 0)
-        dz = dz.to(dy.dtype)
-        return dz, (dz.float().sum(0) if want_bias_grad else None)
+    n = dy.shape[1]
+    if n % 8:
+        dy, z = _pad_cols(dy), _pad_cols(z)
     _count(2 if want_bias_grad else 1)
     dz, db = require().act_backward(dy.contiguous(), z.contiguous(), code, True, bool(want_bias_grad))
+    if dz.shape[1] != n:
+        dz = dz[:, :n].contiguous()
+        db = db[:n].contiguous() if want_bias_grad else db
     return dz, (db if want_bias_grad else None)
 
 
 def column_sum(x):
-    if x.shape[1] % 8 != 0:
-        return x.float().sum(0)
+    n = x.shape[1]
     _count(2)
-    return require().act_backward(x.contiguous(), None, 0, False, True)[1]
+    s = require().act_backward(_pad_cols(x).contiguous(), None, 0, False, True)[1]
+    return s[:n].contiguous() if s.shape[0] != n else s
 
 
 def _f32(t):
@@ -131,63 +147,45 @@ def _f32(t):
 
 
 def _norm_ok(x):
-    return x.shape[1] % 8 == 0 and x.shape[1] <= 16384
+    """The layer-norm kernels read rows in 16-byte pieces and keep one row per CTA in registers."""
+    if x.shape[1] % 8 == 0 and x.shape[1] <= 16384:
+        return True
+    raise ValueError(f"the layer-norm kernels need a hidden size that is a multiple of 8 and at most 16384, got "
+                     f"{x.shape[1]} (run this shape in fp32, which takes the PyTorch formulation)")
 
 
 def layer_norm_fwd(x, gamma, beta, eps):
-    if not _norm_ok(x):
-        xf = x.float()
-        mean, var = xf.mean(-1), xf.var(-1, unbiased=False)
-        rstd = torch.rsqrt(var + eps)
-        return (((xf - mean[:, None]) * rstd[:, None]) * gamma.float() + beta.float()).to(x.dtype), mean, rstd
+    _norm_ok(x)
     _count(1)
     return tuple(require().layer_norm_fwd(x.contiguous(), _f32(gamma), _f32(beta), float(eps)))
 
 
 def layer_norm_bwd(dy, x, mean, rstd, gamma):
-    if not _norm_ok(x):
-        xf, dyf = x.float(), dy.float()
-        xhat = (xf - mean[:, None]) * rstd[:, None]
-        g = dyf * gamma.float()
-        dx = (g - g.mean(-1, keepdim=True) - xhat * (g * xhat).mean(-1, keepdim=True)) * rstd[:, None]
-        return dx.to(x.dtype), (dyf * xhat).sum(0), dyf.sum(0)
+    _norm_ok(x)
     _count(2)
     return tuple(require().layer_norm_bwd(dy.contiguous(), x, mean, rstd, _f32(gamma)))
 
 
 def row_moments(x):
-    if not _norm_ok(x):
-        xf = x.float()
-        return torch.stack([xf.sum(-1), (xf * xf).sum(-1)], -1)
+    _norm_ok(x)
     _count(1)
     return require().row_moments(x.contiguous())
 
 
 def norm_apply(x, mean, rstd, gamma, beta):
-    if not _norm_ok(x):
-        y = (x.float() - mean[:, None]) * rstd[:, None]
-        if gamma is not None:
-            y = y * gamma.float() + beta.float()
-        return y.to(x.dtype)
+    _norm_ok(x)
     _count(1)
     return require().norm_apply(x.contiguous(), mean.contiguous(), rstd.contiguous(), _f32(gamma), _f32(beta))
 
 
 def norm_bwd_partials(dy, x, mean, rstd, gamma):
-    if not _norm_ok(x):
-        xhat = (x.float() - mean[:, None]) * rstd[:, None]
-        dyf = dy.float()
-        g = dyf * gamma.float() if gamma is not None else dyf
-        return torch.stack([g.sum(-1), (g * xhat).sum(-1)], -1), (dyf * xhat).sum(0), dyf.sum(0)
+    _norm_ok(x)
     _count(2)
     return tuple(require().norm_bwd_partials(dy.contiguous(), x, mean.contiguous(), rstd.contiguous(), _f32(gamma)))
 
 
 def norm_bwd_apply(dy, x, mean, rstd, gamma, sums, hidden):
-    if not _norm_ok(x):
-        xhat = (x.float() - mean[:, None]) * rstd[:, None]
-        g = dy.float() * gamma.float() if gamma is not None else dy.float()
-        return ((g - sums[:, 0:1] / hidden - xhat * sums[:, 1:2] / hidden) * rstd[:, None]).to(x.dtype)
+    _norm_ok(x)
     _count(1)
     return require().norm_bwd_apply(dy.contiguous(), x, mean.contiguous(), rstd.contiguous(), _f32(gamma),
                                     sums.contiguous(), float(hidden))

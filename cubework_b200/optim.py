@@ -3,7 +3,8 @@
 Replaces ``torch.optim.AdamW`` (benchmark/gpt2/gpt2.py:440, vit/vit.py:477) and ``torch.optim.SGD``
 (benchmark/opt/opt.py:623).  On CUDA one multi-tensor kernel updates the fp32 master parameter, its
 moments and — when the parameter has a low-precision shadow used by the GEMMs — the shadow, so no
-separate cast kernel runs in steady state.  An optional device-side ``grad_scale`` (e.g. the clipping
+separate cast kernel runs in steady state.  Parameters that are themselves 16-bit (the pure 16-bit mode of
+``benchmark/opt/train.py -O3``) take the formula path with fp32 arithmetic per update and no master copy.  An optional device-side ``grad_scale`` (e.g. the clipping
 coefficient) is folded into the same pass.  On the host the update is the textbook formula and matches
 ``torch.optim`` bit-for-bit in fp32.
 """
@@ -48,7 +49,8 @@ class FusedAdamW(torch.optim.Optimizer):
             if not todo:
                 continue
             step = self.state[todo[0]]["step"]
-            if todo[0].is_cuda and ops.kernels_enabled() and all(self.state[p]["step"] == step for p in todo):
+            if todo[0].is_cuda and ops.kernels_enabled() and all(self.state[p]["step"] == step for p in todo) \
+                    and all(p.dtype == torch.float32 for p in todo):
                 ext.require()
                 shadows = [_lowp_shadow(p) for p in todo]
                 ext.multi_adamw(todo, [p.grad for p in todo], [self.state[p]["exp_avg"] for p in todo],
@@ -95,7 +97,7 @@ class FusedSGD(torch.optim.Optimizer):
                     st["momentum_buffer"] = torch.zeros_like(p, dtype=torch.float32)
                     st["fresh"] = True
                 bufs.append(st.get("momentum_buffer"))
-            if todo[0].is_cuda and ops.kernels_enabled():
+            if todo[0].is_cuda and ops.kernels_enabled() and all(p.dtype == torch.float32 for p in todo):
                 ext.require()
                 shadows = [_lowp_shadow(p) for p in todo]
                 first = bool(mom != 0 and self.state[todo[0]].get("fresh", False))

@@ -258,18 +258,24 @@ def fused_gather_gemm_scatter(a, b, trans_a, trans_b, gather_a, gather_b, scatte
     comm_ctas = _push_ctas(push_bytes, M, N, K, max(plan[0] for plan in (ga, gb) if plan is not None) if (ga or gb) else 1)
     ext._count(1)
     STATS["gather_gemm_scatter"] += 1
+    from . import collective
+    prof = collective._profiler
+    ev0 = ev1 = None
+    if prof is not None:
+        ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        ev0.record()
     m.gather_gemm_scatter(a, b, bool(trans_a), bool(trans_b), bias, out, ga_cfg, ga_bufs, ga_flags, gb_cfg, gb_bufs,
                           gb_flags, sc_cfg, sc_stage, sc_flags, comm_ctas, m.status_device_ptr(), _ACT_CODE[act], z,
                           GGS_TRACE)
-    from . import collective
-    if collective._profiler is not None:
+    if prof is not None:
+        ev1.record()
         moved = 0
         for plan, t in ((ga, a), (gb, b)):
             if plan is not None:
                 moved += (plan[0] - 1) * t.numel() * t.element_size()
         if sc is not None:
             moved += (sc[2] - 1) * Ms * Ns * a.element_size()
-        collective._profiler.account("fused_gather_gemm_scatter", moved)
+        prof.account("fused_gather_gemm_scatter", moved, ev0, ev1)
     res = (out, ) if not pre_act_out else (out, z)
     if not keep_gathered:
         return res if pre_act_out else out

@@ -6,8 +6,11 @@ clipping, LR schedule, per-phase timing, progress bar with running loss / lr / t
 summary (loss, step time, samples/s, tokens/s or images/s, model TFLOPS, peak / state / activation memory,
 communication time / share / algorithm bandwidth), optional evaluation with the family's metric, per-rank log
 files.  Added: sharded checkpoint save / resume (``--save_dir``, ``--resume_step``), synthetic data when no
-dataset path is given (the default: these machines have no network), phase timers on CUDA events instead of
-host clocks with device-wide synchronisation.
+dataset path is given (the default: these machines have no network), phase timers (data / fwd / bwd / opt) on CUDA
+events instead of host clocks with device-wide synchronisation.  With ``--dataset_path`` the family's real-data
+pipeline (:mod:`cubework_b200.utils.datasets`) feeds the loop, and ``--eval`` runs a separate pass over the held-out
+split (the reference's ``_test``, train.py:187-270); with synthetic data the evaluation batches come from a second
+generator that the training loop never sees.
 """
 import argparse
 import time
@@ -43,6 +46,11 @@ def get_parser(description, default_model, token_unit="tokens"):
     p.add_argument("--clip", dest="gradient_clipping", type=float, default=0.0)
     p.add_argument("--amp", dest="use_mixed_precision", action="store_true")
     p.add_argument("--amp_dtype", choices=["bf16", "fp16"], default="bf16")
+    p.add_argument("--fp16_initial_scale", type=float, default=2**15)
+    p.add_argument("--fp16_growth_factor", type=float, default=2.0)
+    p.add_argument("--fp16_backoff_factor", type=float, default=0.5)
+    p.add_argument("--fp16_growth_interval", type=int, default=1000)
+    p.add_argument("--num_workers", type=int, default=0, help="data loader workers of the real-data pipelines")
     p.add_argument("--optimizer", choices=["adamw", "sgd"], default=None)
     p.add_argument("--prof_comm", dest="use_comm_profiler", action="store_true")
     p.add_argument("--log_file", default=None)
@@ -63,10 +71,16 @@ def _dp_mean(value):
 
 
 class PhaseTimer:
-    """Accumulates phase durations from CUDA events; one synchronisation per report, none per step."""
+    """Accumulates phase durations from CUDA events; one synchronisation per report, none per step.  A phase is the
+    span between the device reaching its first and its last enqueued operation, so phases overlap nothing and add
+    up to the step."""
 
     def __init__(self, use_cuda):
-        self.use_cuda, self.open, self.spans = use_cuda, {}, {}
+        self.use_cuda = use_cuda
+        self.reset()
+
+    def reset(self):
+        self.open, self.spans = {}, {}
 
     def start(self, name):
         if self.use_cuda:
@@ -91,6 +105,35 @@ class PhaseTimer:
         return {k: sum(v) for k, v in self.spans.items()}
 
 
+def _test(epoch, trainer, test_loader, metric, args, tokens_per_sample, use_cuda, logger):
+    """One pass over the held-out data: mean loss, the family's metric, evaluation throughput (DATA-group totals)."""
+    metric.reset()
+    timer = PhaseTimer(use_cuda)
+    losses, n_batches, samples = [], 0, 0
+    limit = len(test_loader) if hasattr(test_loader, "__len__") else None
+    it = iter(test_loader)
+    timer.start("eval")
+    while limit is None or n_batches < limit:
+        try:
+            batch = next(it)
+        except StopIteration:
+            break
+        out, targets, loss = trainer.evaluate(batch)
+        metric(out, targets, loss)
+        losses.append(loss.detach().float())
+        first = next(v for v in batch.values() if torch.is_tensor(v))
+        samples += first.shape[0]
+        n_batches += 1
+    timer.stop("eval")
+    secs = max(timer.totals().get("eval", 0.0), 1e-9)
+    mean_loss = _dp_mean(torch.stack(losses).mean().item()) if losses else float("nan")
+    total = samples * pm.DATA.world_size
+    logger.info(f"[Epoch {epoch} / Test]: Loss = {mean_loss:.4f} | {metric.name} = {metric.to_str()} | "
+                f"{n_batches} batches, {total / secs:.2f} samples/sec, {total * tokens_per_sample / secs:.1f} "
+                f"{args.token_unit}/sec")
+    return mean_loss
+
+
 def run(args, family):
     """``family`` provides ``build(args) -> (model, criterion, metric, make_batch, tokens_per_sample)``."""
     logger = get_logger()
@@ -105,6 +148,7 @@ def run(args, family):
         model = FullyShardedDataParallel(model, unit_classes=(_g.GPT2Block, _o.OPTDecoderLayer, _v.ViTBlock))
     elif pm.DATA.world_size > 1:
         model = DataParallel(model)
+    flop_tokens = getattr(model, "flop_tokens_per_sample", tokens_per_sample)   # ViT: tokens per image
     numel, numel_local = calc_model_size(model)
     logger.info(f"model {args.model_name}: {numel / 1e6:.1f} M parameters ({numel_local / 1e6:.1f} M on this rank)")
 
@@ -124,15 +168,29 @@ def run(args, family):
     amp_dtype = None
     if args.use_mixed_precision and dev.type == "cuda":
         amp_dtype = torch.bfloat16 if args.amp_dtype == "bf16" else torch.float16
+    timer = PhaseTimer(dev.type == "cuda")
     trainer = Trainer(model, criterion, optimizer, scheduler, amp_dtype=amp_dtype,
-                      clip=args.gradient_clipping or None, accum_steps=accum, forward_fn=family.forward)
+                      clip=args.gradient_clipping or None, accum_steps=accum, forward_fn=family.forward,
+                      scaler_kwargs=dict(init_scale=args.fp16_initial_scale, growth_factor=args.fp16_growth_factor,
+                                         backoff_factor=args.fp16_backoff_factor,
+                                         growth_interval=args.fp16_growth_interval), timer=timer)
     start_step = 0
     if args.resume_step is not None and args.save_dir:
         start_step, _ = checkpoint.load_checkpoint(args.save_dir, args.resume_step, model, optimizer, scheduler,
                                                    trainer.scaler)
         logger.info(f"resumed from step {start_step}")
 
-    loader = cube.utils.SyntheticLoader(lambda g: make_batch(g, micro), n_distinct=4)
+    if args.dataset_path:
+        from cubework_b200.utils.datasets import Cycle
+        train_loader, test_loader = family.build_data(args, micro, model)
+        loader = Cycle(train_loader)
+        logger.info(f"data: {args.dataset_path} ({len(train_loader)} training / {len(test_loader)} test batches "
+                    f"of {micro} per data-parallel rank)")
+    else:
+        loader = cube.utils.SyntheticLoader(lambda g: make_batch(g, micro), n_distinct=4)
+        n_eval = max(1, args.steps_per_epoch // 4)
+        test_loader = cube.utils.SyntheticLoader(lambda g: make_batch(g, micro), n_distinct=min(4, n_eval), seed=4321,
+                                                 length=n_eval)
     profiler = CommProfiler() if args.use_comm_profiler else None
     use_cuda = dev.type == "cuda"
     try:
@@ -148,14 +206,17 @@ def run(args, family):
         if profiler:
             profiler.reset()
             profiler.start()
-        timer = PhaseTimer(use_cuda)
+        timer.reset()
         bar = tqdm(range(args.steps_per_epoch), desc=f"[Epoch {epoch}]") if (tqdm and pm.GLOBAL.rank == 0) else \
             range(args.steps_per_epoch)
         losses = []
         t_epoch = time.perf_counter()
         for _ in bar:
+            timer.start("load")
+            batches = [next(loader) for _ in range(accum)]
+            timer.stop("load")
             timer.start("step")
-            loss = trainer.step([next(loader) for _ in range(accum)])
+            loss = trainer.step(batches)
             timer.stop("step")
             losses.append(loss)
             step += 1
@@ -166,10 +227,12 @@ def run(args, family):
         step_time = tot["step"] / args.steps_per_epoch
         samples = args.global_batch_size * args.steps_per_epoch
         mean_loss = _dp_mean(torch.stack([x.float() for x in losses]).mean().item())
-        msg = (f"[Epoch {epoch} / Train]: Loss = {mean_loss:.4f} | Step time = {step_time:.3f} s | "
+        phases = " / ".join(f"{k} {tot.get(k, 0.0) / args.steps_per_epoch * 1e3:.1f}" for k in ("data", "fwd", "bwd", "opt"))
+        msg = (f"[Epoch {epoch} / Train]: Loss = {mean_loss:.4f} | Step time = {step_time:.3f} s "
+               f"({phases} ms as enqueued) | "
                f"Throughput = {samples / tot['step']:.2f} samples/sec, "
                f"{samples * tokens_per_sample / tot['step']:.1f} {args.token_unit}/sec | TFLOPS = "
-               f"{calc_tflops(numel, args.global_batch_size * tokens_per_sample, step_time, True, args.use_activation_checkpoint):.2f}"
+               f"{calc_tflops(numel, args.global_batch_size * flop_tokens, step_time, True, args.use_activation_checkpoint):.2f}"
                f" | wall = {wall:.1f} s")
         if use_cuda:
             peak = torch.cuda.max_memory_allocated()
@@ -181,11 +244,7 @@ def run(args, family):
                     f"{vol / max(secs, 1e-9) / 1e9:.1f} GB/s algorithm bandwidth")
         logger.info(msg)
         if args.do_validation and (epoch + 1) % args.validation_interval == 0 and metric is not None:
-            metric.reset()
-            for _ in range(max(1, args.steps_per_epoch // 4)):
-                out, targets, loss = trainer.evaluate(next(loader))
-                metric(out, targets, loss)
-            logger.info(f"[Epoch {epoch} / Eval]: {metric.name} = {metric.to_str()}")
+            _test(epoch, trainer, test_loader, metric, args, tokens_per_sample, use_cuda, logger)
         if args.save_dir:
             d = checkpoint.save_checkpoint(args.save_dir, step, model, optimizer, scheduler, trainer.scaler)
             logger.info(f"checkpoint written to {d}")

@@ -8,8 +8,10 @@ Design: instead of rebinding ``torch.distributed`` functions, the collective wra
 report to the active profiler directly.  Every record holds a pair of CUDA events taken on the
 issuing stream; nothing synchronises the host until ``stop()`` (or ``summary()``), where overlapping
 records are merged into busy intervals so concurrent collectives are not double-counted.  Fused
-compute+collective kernels report their own link bytes through :meth:`account` because their
-transfer is not a separate launch.
+compute+collective kernels report their own link bytes through :meth:`account`, with a pair of
+events around the launch: their transfer is not a separate launch, so their time (``fused_seconds``
+in :meth:`summary`) is the kernels' whole duration - product and exchange overlapped - and is kept
+apart from the time of the stand-alone collectives.
 """
 import time
 
@@ -29,6 +31,7 @@ class CommProfiler(object):
         self.volume = 0
         self.records = []       # (kind, bytes, start, end) with CUDA events or host times
         self.fused_bytes = 0
+        self.fused_records = []  # (start event, end event) of fused compute+collective launches
         self.by_kind = {}
 
     # -- called by cubework_b200.parallel.collective ------------------------------------------
@@ -55,8 +58,10 @@ class CommProfiler(object):
         else:
             rec[3] = time.perf_counter()
 
-    def account(self, kind, nbytes):
-        """Link bytes moved inside a fused kernel (no separate time: it overlaps the GEMM)."""
+    def account(self, kind, nbytes, start=None, end=None):
+        """Link bytes moved inside a fused kernel; ``start`` / ``end`` are CUDA events recorded around its launch."""
+        if start is not None and end is not None:
+            self.fused_records.append((start, end))
         self.ops += 1
         self.volume += nbytes
         self.fused_bytes += nbytes
@@ -93,8 +98,15 @@ class CommProfiler(object):
             self._active = False
         return self.ops, self.volume, self._seconds()
 
+    def _fused_seconds(self):
+        if not self.fused_records:
+            return 0.0
+        torch.cuda.synchronize()
+        return sum(a.elapsed_time(b) for a, b in self.fused_records) / 1e3
+
     def summary(self):
         secs = self._seconds()
         return dict(ops=self.ops, bytes=self.volume, seconds=secs, fused_bytes=self.fused_bytes,
+                    fused_seconds=self._fused_seconds(),
                     algo_gbps=(self.volume - self.fused_bytes) / secs / 1e9 if secs > 0 else 0.0,
                     by_kind={k: tuple(v) for k, v in self.by_kind.items()})

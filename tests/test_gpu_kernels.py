@@ -60,6 +60,31 @@ def test_gemm_epilogues(act, N):
     assert _rel_err(y32, y_ref) < 1e-4
 
 
+@pytest.mark.parametrize("trans_a,trans_b", [(False, True), (False, False), (True, False), (True, True)])
+def test_gemm_unaligned_extents_are_padded(trans_a, trans_b):
+    """Extents that are not multiples of eight elements (TMA needs 16-byte row pitches) run on the same kernel
+    after zero padding; no library GEMM is involved."""
+    ops, ext = _ops()
+    torch.manual_seed(5)
+    M, N, K = 203, 61, 100
+    a = torch.randn((K, M) if trans_a else (M, K), device=DEV, dtype=torch.bfloat16)
+    b = torch.randn((N, K) if trans_b else (K, N), device=DEV, dtype=torch.bfloat16)
+    bias = torch.randn(N, device=DEV)
+    ref = (a.float().t() if trans_a else a.float()) @ (b.float().t() if trans_b else b.float()) + bias
+    before = ext.launch_count()
+    y, z = ext.gemm(a, b, trans_a, trans_b, bias, "relu", torch.bfloat16, True)
+    assert ext.launch_count() == before + 1
+    ext.check_status()
+    assert y.shape == (M, N) and z.shape == (M, N) and y.is_contiguous()
+    assert _rel_err(z, ref) < 6e-3 and _rel_err(y, torch.relu(ref)) < 6e-3
+    dz, db = ext.act_backward(y, z, "relu", True)
+    assert dz.shape == (M, N) and _rel_err(db, (y.float() * (z.float() > 0)).sum(0)) < 5e-3
+    assert _rel_err(ext.column_sum(y), y.float().sum(0)) < 5e-3
+    with pytest.raises(ValueError):
+        ops.layer_norm_fwd(torch.randn(4, 60, device=DEV, dtype=torch.bfloat16), torch.ones(60, device=DEV),
+                           torch.zeros(60, device=DEV), 1e-5)
+
+
 @pytest.mark.parametrize("tokens,out_f,in_f", [(4096, 200, 328), (8192, 1600, 1600), (2048, 72, 104)])
 def test_gemm_split_k_weight_gradient_shape(tokens, out_f, in_f):
     """fp32 weight gradients: few tiles with a long K are split (8 ways / 3 ways for the first two shapes) and summed
