@@ -4,7 +4,6 @@ import math
 
 import torch
 import torch.nn as nn
-import torch.utils.checkpoint as ckpt
 
 from .. import module as cube_nn
 from .. import ops
@@ -65,10 +64,68 @@ class MLP(nn.Module):
         return self.dropout(self.dense_2(self.inner_dropout(self.dense_1(x))))
 
 
+class _Recompute(torch.autograd.Function):
+    """Activation checkpointing of one block (reference: ``torch.utils.checkpoint`` per block, gpt2.py:190-194,
+    opt.py:221-224, vit.py:201-205): the forward keeps only the block's inputs, the backward re-runs the block.
+
+    Two things the library routine does not do: the random streams of every process-group kind
+    (``with seed(mode)`` regions, e.g. dropout on sharded activations) are rewound together with the default
+    generators, so the re-run draws the same masks; and while the block is re-run
+    :func:`cubework_b200.parallel.ops_1d.recomputing` is set, which lets the block's last linear layer skip its
+    product and collective - nothing in the backward reads the block's output.
+    """
+
+    @staticmethod
+    def forward(ctx, fn, *args):
+        from ..utils.checkpoint import _rng_states
+        ctx.fn = fn
+        ctx.rng = _rng_states()
+        ctx.autocast = {dev: (torch.is_autocast_enabled(dev), torch.get_autocast_dtype(dev)) for dev in ("cuda", "cpu")}
+        ctx.is_tensor = [torch.is_tensor(a) for a in args]
+        ctx.consts = [None if t else a for a, t in zip(args, ctx.is_tensor)]
+        ctx.save_for_backward(*[a for a in args if torch.is_tensor(a)])
+        with torch.no_grad():
+            return fn(*args)
+
+    @staticmethod
+    def backward(ctx, *grads):
+        from ..parallel import ops_1d
+        from ..utils.checkpoint import _rng_states, _set_rng_states
+        saved = iter(ctx.saved_tensors)
+        args = []
+        for t, c in zip(ctx.is_tensor, ctx.consts):
+            if t:
+                a = next(saved).detach()
+                a.requires_grad_(a.is_floating_point())
+                args.append(a)
+            else:
+                args.append(c)
+        now = _rng_states()
+        _set_rng_states(ctx.rng)
+        try:
+            with torch.enable_grad(), torch.autocast("cuda", dtype=ctx.autocast["cuda"][1], enabled=ctx.autocast["cuda"][0]), \
+                    torch.autocast("cpu", dtype=ctx.autocast["cpu"][1], enabled=ctx.autocast["cpu"][0]), \
+                    ops_1d.recomputing():
+                out = ctx.fn(*args)
+        finally:
+            _set_rng_states(now)
+        outs = out if isinstance(out, (tuple, list)) else (out, )
+        pairs = [(o, g) for o, g in zip(outs, grads) if torch.is_tensor(o) and o.requires_grad and g is not None]
+        torch.autograd.backward([o for o, _ in pairs], [g for _, g in pairs])
+        return (None, ) + tuple(a.grad if (torch.is_tensor(a) and a.requires_grad) else None for a in args)
+
+
 def maybe_checkpoint(fn, enabled, *args):
-    if enabled and torch.is_grad_enabled():
-        return ckpt.checkpoint(fn, *args, use_reentrant=False)
+    if enabled and torch.is_grad_enabled() and any(torch.is_tensor(a) and a.requires_grad for a in args):
+        return _Recompute.apply(fn, *args)
     return fn(*args)
+
+
+def mark_block_output(linear):
+    """Declare that the output of ``linear`` (a façade ``Linear``) only leaves its checkpointed block through
+    value-free operations (dropout, residual add), so a re-run of the block for its gradients may skip the product."""
+    inner = getattr(linear, "linear", linear)
+    inner.output_unused_in_recompute = True
 
 
 def key_bias_from_mask(attention_mask, dtype=torch.float32):

@@ -11,7 +11,7 @@ import torch.nn as nn
 
 from .. import module as cube_nn
 from ..parallel.loss import IGNORE_INDEX
-from .common import MLP, SelfAttention, key_bias_from_mask, maybe_checkpoint, normal_init
+from .common import MLP, SelfAttention, key_bias_from_mask, mark_block_output, maybe_checkpoint, normal_init
 
 
 class GPT2Embedding(nn.Module):
@@ -50,15 +50,28 @@ class GPT2Block(nn.Module):
                                   qkv_kw=wi, out_kw=wo, **sp)
         self.norm2 = cube_nn.LayerNorm(hidden_size, eps=layernorm_epsilon, **sp)
         self.mlp = MLP(hidden_size, intermediate_size, "gelu", dropout, bias=bias, kw1=wi, kw2=wo, **sp)
+        mark_block_output(self.mlp.dense_2)     # its output only feeds dropout and the residual add
 
-    def _forward(self, x, key_bias=None):
-        h = self.norm1(x)
-        x = (h if self.apply_post_layernorm else x) + self.attn(h, key_bias)
-        h = self.norm2(x)
-        return (h if self.apply_post_layernorm else x) + self.mlp(h)
+    def _forward(self, x, pending, key_bias=None):
+        """``x``: residual stream; ``pending``: the previous block's contribution that has not been added yet (or
+        None).  Returns ``(stream, pending)`` again, so every residual add is done by the layer norm that follows it
+        (one kernel computes the sum and its normalised value)."""
+        if self.apply_post_layernorm:
+            if pending is not None:
+                x = x + pending
+            h = self.norm1(x)
+            x = h + self.attn(h, key_bias)
+            h = self.norm2(x)
+            return h, self.mlp(h)
+        if pending is None:
+            h = self.norm1(x)
+        else:
+            x, h = self.norm1(x, residual=pending)
+        x, h = self.norm2(x, residual=self.attn(h, key_bias))
+        return x, self.mlp(h)
 
-    def forward(self, x, key_bias=None):
-        return maybe_checkpoint(self._forward, self.checkpoint and self.training, x, key_bias)
+    def forward(self, x, pending=None, key_bias=None):
+        return maybe_checkpoint(self._forward, self.checkpoint and self.training, x, pending, key_bias)
 
 
 class GPT2LMLoss(nn.Module):
@@ -105,9 +118,11 @@ class GPT2(nn.Module):
                              f"parallel size ({self.sp_size})")
         x = self.embed(input_ids)
         key_bias = key_bias_from_mask(attention_mask)
+        pending = None
         for block in self.blocks:
-            x = block(x, key_bias)
-        return self.head(self.norm(x))
+            x, pending = block(x, pending, key_bias)
+        h = self.norm(x) if pending is None else self.norm(x, residual=pending)[1]
+        return self.head(h)
 
 
 _PRESETS = {

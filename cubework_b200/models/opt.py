@@ -13,7 +13,7 @@ import torch.nn as nn
 from .. import module as cube_nn
 from .. import ops
 from ..parallel.loss import IGNORE_INDEX
-from .common import MLP, SelfAttention, key_bias_from_mask, maybe_checkpoint, normal_init
+from .common import MLP, SelfAttention, key_bias_from_mask, mark_block_output, maybe_checkpoint, normal_init
 
 
 def _init_kw(init_std):
@@ -71,6 +71,8 @@ class OPTDecoderLayer(nn.Module):
         self.self_attn_layer_norm = cube_nn.LayerNorm(hidden_size, dtype=dtype)
         kw = dict(dtype=dtype, **_init_kw(init_std))
         self.ffn = MLP(hidden_size, ffn_dim, activation_function, dropout, kw1=kw, kw2=kw)
+        if do_layer_norm_before:                # (the post-LN layout normalises the sum, which needs its value)
+            mark_block_output(self.ffn.dense_2)
         self.final_layer_norm = cube_nn.LayerNorm(hidden_size, dtype=dtype)
 
     fc1 = property(lambda self: self.ffn.dense_1)

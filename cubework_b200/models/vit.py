@@ -10,7 +10,7 @@ import torch
 import torch.nn as nn
 
 from .. import module as cube_nn
-from .common import MLP, SelfAttention, maybe_checkpoint
+from .common import MLP, SelfAttention, mark_block_output, maybe_checkpoint
 
 
 def _lin_kw():
@@ -62,6 +62,7 @@ class ViTBlock(nn.Module):
         self.norm2 = cube_nn.LayerNorm(hidden_size, eps=layernorm_epsilon)
         self.mlp = MLP(hidden_size, intermediate_size, "gelu", dropout, bias=bias, kw1=_lin_kw(), kw2=_lin_kw(),
                        inner_dropout=dropout)
+        mark_block_output(self.mlp.dense_2)
 
     def _forward(self, x):
         x = x + self.drop_path(self.attn(self.norm1(x)))

@@ -165,10 +165,14 @@ def column_sum(x: torch.Tensor) -> torch.Tensor:
 # ---------------------------------------------------------------------------------------------------
 # LayerNorm (local statistics; the 2D/3D layers pass partial sums through a collective in between)
 # ---------------------------------------------------------------------------------------------------
-def layer_norm_fwd(x2d, gamma, beta, eps):
-    """Returns ``(y, mean, rstd)``; statistics in fp32."""
+def layer_norm_fwd(x2d, gamma, beta, eps, residual=None):
+    """Returns ``(y, mean, rstd)``; statistics in fp32.  With ``residual`` the norm is that of ``x + residual``
+    (rounded to the tensors' dtype) and the sum is returned as a fourth value."""
     if use_kernels(x2d):
-        return ext.layer_norm_fwd(x2d, gamma, beta, eps)
+        return ext.layer_norm_fwd(x2d, gamma, beta, eps, residual)
+    if residual is not None:
+        total = x2d + residual
+        return layer_norm_fwd(total, gamma, beta, eps) + (total, )
     xf = x2d.float()
     mean = xf.mean(-1)
     var = xf.var(-1, unbiased=False)
@@ -177,10 +181,14 @@ def layer_norm_fwd(x2d, gamma, beta, eps):
     return y.to(x2d.dtype), mean, rstd
 
 
-def layer_norm_bwd(dy2d, x2d, mean, rstd, gamma):
-    """Returns ``(dx, dgamma, dbeta)``; parameter gradients in fp32."""
+def layer_norm_bwd(dy2d, x2d, mean, rstd, gamma, dres=None):
+    """Returns ``(dx, dgamma, dbeta)``; parameter gradients in fp32.  ``dres`` (a gradient that reaches the
+    normalised tensor by another path, e.g. the residual connection) is added to ``dx``."""
     if use_kernels(x2d):
-        return ext.layer_norm_bwd(dy2d, x2d, mean, rstd, gamma)
+        return ext.layer_norm_bwd(dy2d, x2d, mean, rstd, gamma, dres)
+    if dres is not None:
+        dx, dg, db = layer_norm_bwd(dy2d, x2d, mean, rstd, gamma)
+        return dx + dres.to(dx.dtype), dg, db
     xf, dyf = x2d.float(), dy2d.float()
     xhat = (xf - mean[:, None]) * rstd[:, None]
     dgamma = (dyf * xhat).sum(0)

@@ -12,6 +12,10 @@ namespace cw {
 std::vector<torch::Tensor> layer_norm_fwd(torch::Tensor x, torch::Tensor gamma, torch::Tensor beta, double eps);
 std::vector<torch::Tensor> layer_norm_bwd(torch::Tensor dy, torch::Tensor x, torch::Tensor mean, torch::Tensor rstd,
                                           torch::Tensor gamma);
+std::vector<torch::Tensor> layer_norm_fwd_res(torch::Tensor x, c10::optional<torch::Tensor> residual, torch::Tensor gamma,
+                                              torch::Tensor beta, double eps);
+std::vector<torch::Tensor> layer_norm_bwd_res(torch::Tensor dy, torch::Tensor x, torch::Tensor mean, torch::Tensor rstd,
+                                              torch::Tensor gamma, c10::optional<torch::Tensor> dres);
 torch::Tensor norm_apply(torch::Tensor x, torch::Tensor mean, torch::Tensor rstd, c10::optional<torch::Tensor> gamma,
                          c10::optional<torch::Tensor> beta);
 torch::Tensor row_moments(torch::Tensor x);
@@ -122,6 +126,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("read_status", &cw::read_status);
   m.def("layer_norm_fwd", &cw::layer_norm_fwd);
   m.def("layer_norm_bwd", &cw::layer_norm_bwd);
+  m.def("layer_norm_fwd_res", &cw::layer_norm_fwd_res);
+  m.def("layer_norm_bwd_res", &cw::layer_norm_bwd_res);
   m.def("norm_apply", &cw::norm_apply);
   m.def("row_moments", &cw::row_moments);
   m.def("norm_bwd_partials", &cw::norm_bwd_partials);

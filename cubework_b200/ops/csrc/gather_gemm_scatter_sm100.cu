@@ -753,18 +753,32 @@ gather_gemm_scatter_kernel(const __grid_constant__ CUtensorMap tma_a, const __gr
         }
         if (!live) continue;
         if (scat) {
-          for (int src = 0; src < p.sn; ++src) {
-            if (src == p.sme) continue;
-            const InT* part = stage + static_cast<size_t>(src) * kTileElems;
-            uint4 pc[8];
+          // the peers' partials: the loads of the next source are in flight while the current one is added
+          uint4 pa[8], pb[8];
+          auto next_src = [&](int s) { ++s; return s == p.sme ? s + 1 : s; };
+          auto fetch = [&](uint4 (&dst)[8], int s) {
 #pragma unroll
-            for (int j = 0; j < 8; ++j) pc[j] = ld_cg16(part + staged_off_v2(r, cq, j));
+            for (int j = 0; j < 8; ++j) dst[j] = ld_cg16(stage + static_cast<size_t>(s) * kTileElems + staged_off_v2(r, cq, j));
+          };
+          auto add = [&](const uint4 (&srcv)[8]) {
 #pragma unroll
             for (int j = 0; j < 8; ++j) {
-              const InT* hh = reinterpret_cast<const InT*>(&pc[j]);
+              const InT* hh = reinterpret_cast<const InT*>(&srcv[j]);
 #pragma unroll
               for (int e = 0; e < 8; ++e) v[j * 8 + e] += tof(hh[e]);
             }
+          };
+          int s0 = next_src(-1);
+          fetch(pa, s0);
+          for (;;) {
+            const int s1 = next_src(s0);
+            if (s1 < p.sn) fetch(pb, s1);
+            add(pa);
+            if (s1 >= p.sn) break;
+            s0 = next_src(s1);
+            if (s0 < p.sn) fetch(pa, s0);
+            add(pb);
+            if (s0 >= p.sn) break;
           }
         }
         if (p.bias != nullptr) {

@@ -393,7 +393,9 @@ static void dispatch_major(bool ak, bool bk, const CUtensorMap& ta, const CUtens
 void gemm_launch(const GemmArgs& g, cudaStream_t stream) {
   const bool a_kmajor = !g.trans_a;
   const bool b_kmajor = g.trans_b;
-  const int bn = ((g.N <= 128 || (g.N % 256 != 0 && g.N % 256 <= 128 && g.N < 1024)) ? 128 : 256);
+  // 128-wide tiles read 128 B of shared memory per tensor-core clock against 96 B for 256-wide ones and lose even
+  // where they waste fewer columns (N = 800: 115 us with 7 tiles of 128, 83 us with 4 tiles of 256)
+  const int bn = g.N <= 128 ? 128 : 256;
   const int tiles = ((g.M + kBM - 1) / kBM) * ((g.N + bn - 1) / bn);
   const int kb_total = (g.K + kBK - 1) / kBK;
   int sms = g.num_sms;

@@ -184,6 +184,193 @@ __global__ void __launch_bounds__(kNT) ln_bwd_kernel(const T* __restrict__ dy, c
   }
 }
 
+// ---------------------------------------------------------------------------------------------------------
+// Warp-per-row layer norm for hidden sizes up to 2048: a row lives in one warp's registers (NV 16-byte vectors
+// per lane), the two statistics are warp shuffles, and nothing synchronises the CTA, so eight rows per CTA are in
+// flight with all their loads outstanding.  Optionally fused with the residual add in front of the norm
+// (reference: `x = x + dropout(...)` followed by `norm(x)`, benchmark/gpt2/gpt2.py:179-186): forward writes the sum
+// and its normalised value, backward adds the gradient that reaches the sum directly.
+constexpr int kWarpRows = 8;                 // warps (rows in flight) per CTA
+
+template <typename T>
+__device__ __forceinline__ void unpack8(const uint4& raw, float (&f)[8]) {
+  const T* h = reinterpret_cast<const T*>(&raw);
+#pragma unroll
+  for (int i = 0; i < 8; ++i) f[i] = to_f(h[i]);
+}
+template <typename T>
+__device__ __forceinline__ uint4 pack8(const float (&f)[8]) {
+  uint4 raw;
+  T* h = reinterpret_cast<T*>(&raw);
+#pragma unroll
+  for (int i = 0; i < 8; ++i) h[i] = from_f<T>(f[i]);
+  return raw;
+}
+
+template <typename T, int NV, bool HAS_RES>
+__global__ void __launch_bounds__(32 * kWarpRows)
+ln_fwd_warp_kernel(const T* __restrict__ x, const T* __restrict__ res, const float* __restrict__ gamma,
+                   const float* __restrict__ beta, T* __restrict__ sum_out, T* __restrict__ y, float* __restrict__ mean_o,
+                   float* __restrict__ rstd_o, int rows, int H, float eps) {
+  const int lane = threadIdx.x & 31;
+  const int warp = blockIdx.x * kWarpRows + (threadIdx.x >> 5);
+  const int nwarps = gridDim.x * kWarpRows;
+  const float inv_h = 1.0f / H;
+  for (int row = warp; row < rows; row += nwarps) {
+    const size_t base = static_cast<size_t>(row) * H;
+    uint4 raw[NV];
+#pragma unroll
+    for (int v = 0; v < NV; ++v) {
+      const int c = (v * 32 + lane) * 8;
+      raw[v] = c < H ? *reinterpret_cast<const uint4*>(x + base + c) : make_uint4(0, 0, 0, 0);
+    }
+    if (HAS_RES) {
+#pragma unroll
+      for (int v = 0; v < NV; ++v) {
+        const int c = (v * 32 + lane) * 8;
+        if (c < H) {
+          const uint4 r = *reinterpret_cast<const uint4*>(res + base + c);
+          float a[8], b[8];
+          unpack8<T>(raw[v], a);
+          unpack8<T>(r, b);
+#pragma unroll
+          for (int i = 0; i < 8; ++i) a[i] += b[i];
+          raw[v] = pack8<T>(a);                       // the normalised value is that of the stored (rounded) sum
+          *reinterpret_cast<uint4*>(sum_out + base + c) = raw[v];
+        }
+      }
+    }
+    float s = 0.f;
+#pragma unroll
+    for (int v = 0; v < NV; ++v) {
+      float f[8];
+      unpack8<T>(raw[v], f);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) s += f[i];
+    }
+    const float mean = warp_sum(s) * inv_h;
+    float q = 0.f;
+#pragma unroll
+    for (int v = 0; v < NV; ++v) {
+      if ((v * 32 + lane) * 8 < H) {
+        float f[8];
+        unpack8<T>(raw[v], f);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) { const float d = f[i] - mean; q += d * d; }
+      }
+    }
+    const float rstd = rsqrtf(warp_sum(q) * inv_h + eps);
+    if (lane == 0) { mean_o[row] = mean; rstd_o[row] = rstd; }
+#pragma unroll
+    for (int v = 0; v < NV; ++v) {
+      const int c = (v * 32 + lane) * 8;
+      if (c < H) {
+        float f[8];
+        unpack8<T>(raw[v], f);
+        const float4 g0 = __ldg(reinterpret_cast<const float4*>(gamma + c)), g1 = __ldg(reinterpret_cast<const float4*>(gamma + c + 4));
+        const float4 b0 = __ldg(reinterpret_cast<const float4*>(beta + c)), b1 = __ldg(reinterpret_cast<const float4*>(beta + c + 4));
+        const float gg[8] = {g0.x, g0.y, g0.z, g0.w, g1.x, g1.y, g1.z, g1.w};
+        const float bb[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
+#pragma unroll
+        for (int i = 0; i < 8; ++i) f[i] = (f[i] - mean) * rstd * gg[i] + bb[i];
+        *reinterpret_cast<uint4*>(y + base + c) = pack8<T>(f);
+      }
+    }
+  }
+}
+
+// Backward of the above.  Each lane keeps dgamma / dbeta of its columns in registers over all the rows of its warp;
+// the eight warps of a CTA combine them in shared memory and the CTA writes one partial row (summed by colsum2).
+template <typename T, int NV, bool HAS_RES>
+__global__ void __launch_bounds__(32 * kWarpRows, 1)
+ln_bwd_warp_kernel(const T* __restrict__ dy, const T* __restrict__ x, const float* __restrict__ mean,
+                   const float* __restrict__ rstd, const float* __restrict__ gamma, const T* __restrict__ dres,
+                   T* __restrict__ dx, float* __restrict__ part_dgamma, float* __restrict__ part_dbeta, int rows, int H) {
+  extern __shared__ float sacc[];            // [2][H]
+  const int lane = threadIdx.x & 31;
+  const int warp = blockIdx.x * kWarpRows + (threadIdx.x >> 5);
+  const int nwarps = gridDim.x * kWarpRows;
+  const float inv_h = 1.0f / H;
+  float dg[NV][8], db[NV][8];
+#pragma unroll
+  for (int v = 0; v < NV; ++v)
+#pragma unroll
+    for (int i = 0; i < 8; ++i) { dg[v][i] = 0.f; db[v][i] = 0.f; }
+  for (int i = threadIdx.x; i < 2 * H; i += blockDim.x) sacc[i] = 0.f;
+
+  for (int row = warp; row < rows; row += nwarps) {
+    const size_t base = static_cast<size_t>(row) * H;
+    uint4 xr[NV], gr[NV];
+#pragma unroll
+    for (int v = 0; v < NV; ++v) {
+      const int c = (v * 32 + lane) * 8;
+      const bool ok = c < H;
+      xr[v] = ok ? *reinterpret_cast<const uint4*>(x + base + c) : make_uint4(0, 0, 0, 0);
+      gr[v] = ok ? *reinterpret_cast<const uint4*>(dy + base + c) : make_uint4(0, 0, 0, 0);
+    }
+    const float mu = mean[row], rs = rstd[row];
+    float s1 = 0.f, s2 = 0.f;
+#pragma unroll
+    for (int v = 0; v < NV; ++v) {
+      const int c = (v * 32 + lane) * 8;
+      if (c < H) {
+        float xf[8], df[8];
+        unpack8<T>(xr[v], xf);
+        unpack8<T>(gr[v], df);
+        const float4 g0 = __ldg(reinterpret_cast<const float4*>(gamma + c)), g1 = __ldg(reinterpret_cast<const float4*>(gamma + c + 4));
+        const float gg[8] = {g0.x, g0.y, g0.z, g0.w, g1.x, g1.y, g1.z, g1.w};
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          const float xhat = (xf[i] - mu) * rs;
+          dg[v][i] += df[i] * xhat;
+          db[v][i] += df[i];
+          const float g = df[i] * gg[i];
+          s1 += g;
+          s2 += g * xhat;
+        }
+      }
+    }
+    const float m1 = warp_sum(s1) * inv_h, m2 = warp_sum(s2) * inv_h;
+#pragma unroll
+    for (int v = 0; v < NV; ++v) {
+      const int c = (v * 32 + lane) * 8;
+      if (c < H) {
+        float xf[8], df[8], o[8];
+        unpack8<T>(xr[v], xf);
+        unpack8<T>(gr[v], df);
+        const float4 g0 = __ldg(reinterpret_cast<const float4*>(gamma + c)), g1 = __ldg(reinterpret_cast<const float4*>(gamma + c + 4));
+        const float gg[8] = {g0.x, g0.y, g0.z, g0.w, g1.x, g1.y, g1.z, g1.w};
+#pragma unroll
+        for (int i = 0; i < 8; ++i) o[i] = (df[i] * gg[i] - m1 - (xf[i] - mu) * rs * m2) * rs;
+        if (HAS_RES) {
+          float rf[8];
+          unpack8<T>(*reinterpret_cast<const uint4*>(dres + base + c), rf);
+#pragma unroll
+          for (int i = 0; i < 8; ++i) o[i] += rf[i];
+        }
+        *reinterpret_cast<uint4*>(dx + base + c) = pack8<T>(o);
+      }
+    }
+  }
+  __syncthreads();
+#pragma unroll
+  for (int v = 0; v < NV; ++v) {
+    const int c = (v * 32 + lane) * 8;
+    if (c < H) {
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        atomicAdd(&sacc[c + i], dg[v][i]);
+        atomicAdd(&sacc[H + c + i], db[v][i]);
+      }
+    }
+  }
+  __syncthreads();
+  for (int i = threadIdx.x; i < H; i += blockDim.x) {
+    part_dgamma[static_cast<size_t>(blockIdx.x) * H + i] = sacc[i];
+    part_dbeta[static_cast<size_t>(blockIdx.x) * H + i] = sacc[H + i];
+  }
+}
+
 // out[c] = sum_p part[p, c] for two partial buffers at once.
 __global__ void colsum2_kernel(const float* __restrict__ pa, const float* __restrict__ pb, float* __restrict__ oa,
                                float* __restrict__ ob, int P, int H) {
@@ -343,6 +530,120 @@ torch::Tensor norm_bwd_apply(torch::Tensor dy, torch::Tensor x, torch::Tensor me
   ln_bwd_launch<2>(dy, x, mean.data_ptr<float>(), rstd.data_ptr<float>(), fptr(gamma), dx.data_ptr(), sums.data_ptr<float>(),
                    nullptr, nullptr, row_grid(rows), static_cast<float>(hidden), stream);
   return dx;
+}
+
+// ---- warp-per-row path (hidden <= 2048) --------------------------------------------------------------------
+constexpr int kWarpMaxH = 2048;
+#define DISPATCH_NV(H, ...)                                        \
+  {                                                                \
+    const int need_ = ((H) / 8 + 31) / 32;                         \
+    if (need_ <= 1) { constexpr int NV = 1; __VA_ARGS__ }          \
+    else if (need_ <= 2) { constexpr int NV = 2; __VA_ARGS__ }     \
+    else if (need_ <= 4) { constexpr int NV = 4; __VA_ARGS__ }     \
+    else if (need_ <= 7) { constexpr int NV = 7; __VA_ARGS__ }     \
+    else { constexpr int NV = 8; __VA_ARGS__ }                     \
+  }
+#define DISPATCH_16_NV(x, ...)                                     \
+  if ((x).scalar_type() == torch::kBFloat16) {                     \
+    using T = __nv_bfloat16;                                       \
+    DISPATCH_NV((x).size(1), __VA_ARGS__)                          \
+  } else {                                                         \
+    using T = __half;                                              \
+    DISPATCH_NV((x).size(1), __VA_ARGS__)                          \
+  }
+
+static bool warp_path(const torch::Tensor& x) { return x.size(1) <= kWarpMaxH; }
+
+// y = LN(x (+ residual)); returns {y, mean, rstd, sum}: `sum` is x + residual (undefined without a residual).
+std::vector<torch::Tensor> layer_norm_fwd_res(torch::Tensor x, c10::optional<torch::Tensor> residual, torch::Tensor gamma,
+                                              torch::Tensor beta, double eps) {
+  check_rows(x);
+  const bool has_res = residual.has_value() && residual->defined();
+  const int rows = x.size(0), H = x.size(1);
+  TORCH_CHECK(gamma.scalar_type() == torch::kFloat32 && beta.scalar_type() == torch::kFloat32 && gamma.is_contiguous() &&
+              beta.is_contiguous() && gamma.numel() == H && beta.numel() == H, "norm parameters must be contiguous fp32 [H]");
+  torch::Tensor sum;
+  if (has_res) {
+    check_rows(*residual);
+    TORCH_CHECK(residual->sizes() == x.sizes() && residual->scalar_type() == x.scalar_type());
+    if (!warp_path(x)) {                       // wide rows: separate add, then the CTA-per-row kernel
+      sum = x + *residual;
+      auto r = layer_norm_fwd(sum, gamma, beta, eps);
+      r.push_back(sum);
+      return r;
+    }
+    sum = torch::empty_like(x);
+  } else if (!warp_path(x)) {
+    auto r = layer_norm_fwd(x, gamma, beta, eps);
+    r.push_back(torch::Tensor());
+    return r;
+  }
+  auto y = torch::empty_like(x);
+  auto mean = torch::empty({rows}, x.options().dtype(torch::kFloat32));
+  auto rstd = torch::empty({rows}, x.options().dtype(torch::kFloat32));
+  if (rows == 0) return {y, mean, rstd, sum};
+  auto stream = at::cuda::getCurrentCUDAStream();
+  const int sms = at::cuda::getCurrentDeviceProperties()->multiProcessorCount;
+  const int grid = std::max(1, std::min((rows + kWarpRows - 1) / kWarpRows, sms * 6));
+  if (has_res) {
+    DISPATCH_16_NV(x, ln_fwd_warp_kernel<T, NV, true><<<grid, 32 * kWarpRows, 0, stream>>>(
+                          reinterpret_cast<const T*>(x.data_ptr()), reinterpret_cast<const T*>(residual->data_ptr()),
+                          gamma.data_ptr<float>(), beta.data_ptr<float>(), reinterpret_cast<T*>(sum.data_ptr()),
+                          reinterpret_cast<T*>(y.data_ptr()), mean.data_ptr<float>(), rstd.data_ptr<float>(), rows, H,
+                          static_cast<float>(eps));)
+  } else {
+    DISPATCH_16_NV(x, ln_fwd_warp_kernel<T, NV, false><<<grid, 32 * kWarpRows, 0, stream>>>(
+                          reinterpret_cast<const T*>(x.data_ptr()), nullptr, gamma.data_ptr<float>(), beta.data_ptr<float>(),
+                          nullptr, reinterpret_cast<T*>(y.data_ptr()), mean.data_ptr<float>(), rstd.data_ptr<float>(), rows, H,
+                          static_cast<float>(eps));)
+  }
+  C10_CUDA_KERNEL_LAUNCH_CHECK();
+  return {y, mean, rstd, sum};
+}
+
+// {dx, dgamma, dbeta} with dx = LN'(dy) (+ dres, the gradient that reaches the normalised tensor directly).
+std::vector<torch::Tensor> layer_norm_bwd_res(torch::Tensor dy, torch::Tensor x, torch::Tensor mean, torch::Tensor rstd,
+                                              torch::Tensor gamma, c10::optional<torch::Tensor> dres) {
+  check_rows(x);
+  check_rows(dy);
+  const bool has_res = dres.has_value() && dres->defined();
+  if (!warp_path(x)) {
+    auto r = layer_norm_bwd(dy, x, mean, rstd, gamma);
+    if (has_res) r[0].add_(*dres);
+    return r;
+  }
+  const int rows = x.size(0), H = x.size(1);
+  TORCH_CHECK(gamma.scalar_type() == torch::kFloat32 && gamma.is_contiguous() && gamma.numel() == H);
+  if (has_res) {
+    check_rows(*dres);
+    TORCH_CHECK(dres->sizes() == x.sizes() && dres->scalar_type() == x.scalar_type());
+  }
+  auto dx = torch::empty_like(x);
+  auto f32 = x.options().dtype(torch::kFloat32);
+  auto dgamma = torch::zeros({H}, f32), dbeta = torch::zeros({H}, f32);
+  if (rows == 0) return {dx, dgamma, dbeta};
+  auto stream = at::cuda::getCurrentCUDAStream();
+  const int sms = at::cuda::getCurrentDeviceProperties()->multiProcessorCount;
+  const int grid = std::max(1, std::min((rows + kWarpRows - 1) / kWarpRows, sms));
+  auto scratch = torch::empty({2, grid, H}, f32);
+  float* pdg = scratch.data_ptr<float>();
+  float* pdb = pdg + static_cast<size_t>(grid) * H;
+  const size_t smem = 2 * static_cast<size_t>(H) * sizeof(float);
+  if (has_res) {
+    DISPATCH_16_NV(x, ln_bwd_warp_kernel<T, NV, true><<<grid, 32 * kWarpRows, smem, stream>>>(
+                          reinterpret_cast<const T*>(dy.data_ptr()), reinterpret_cast<const T*>(x.data_ptr()),
+                          mean.data_ptr<float>(), rstd.data_ptr<float>(), gamma.data_ptr<float>(),
+                          reinterpret_cast<const T*>(dres->data_ptr()), reinterpret_cast<T*>(dx.data_ptr()), pdg, pdb, rows, H);)
+  } else {
+    DISPATCH_16_NV(x, ln_bwd_warp_kernel<T, NV, false><<<grid, 32 * kWarpRows, smem, stream>>>(
+                          reinterpret_cast<const T*>(dy.data_ptr()), reinterpret_cast<const T*>(x.data_ptr()),
+                          mean.data_ptr<float>(), rstd.data_ptr<float>(), gamma.data_ptr<float>(), nullptr,
+                          reinterpret_cast<T*>(dx.data_ptr()), pdg, pdb, rows, H);)
+  }
+  C10_CUDA_KERNEL_LAUNCH_CHECK();
+  colsum2_kernel<<<(H + 255) / 256, 256, 0, stream>>>(pdg, pdb, dgamma.data_ptr<float>(), dbeta.data_ptr<float>(), grid, H);
+  C10_CUDA_KERNEL_LAUNCH_CHECK();
+  return {dx, dgamma, dbeta};
 }
 
 }  // namespace cw

@@ -154,16 +154,21 @@ def _norm_ok(x):
                      f"{x.shape[1]} (run this shape in fp32, which takes the PyTorch formulation)")
 
 
-def layer_norm_fwd(x, gamma, beta, eps):
+def layer_norm_fwd(x, gamma, beta, eps, residual=None):
+    """``(y, mean, rstd)``, or ``(y, mean, rstd, x + residual)`` when a residual is given (added in the same kernel)."""
     _norm_ok(x)
     _count(1)
-    return tuple(require().layer_norm_fwd(x.contiguous(), _f32(gamma), _f32(beta), float(eps)))
+    y, mean, rstd, total = require().layer_norm_fwd_res(x.contiguous(), None if residual is None else residual.contiguous(),
+                                                        _f32(gamma), _f32(beta), float(eps))
+    return (y, mean, rstd) if residual is None else (y, mean, rstd, total)
 
 
-def layer_norm_bwd(dy, x, mean, rstd, gamma):
+def layer_norm_bwd(dy, x, mean, rstd, gamma, dres=None):
+    """``(dx, dgamma, dbeta)``; ``dres`` (optional) is added to ``dx`` in the same kernel."""
     _norm_ok(x)
     _count(2)
-    return tuple(require().layer_norm_bwd(dy.contiguous(), x, mean, rstd, _f32(gamma)))
+    return tuple(require().layer_norm_bwd_res(dy.contiguous(), x, mean, rstd, _f32(gamma),
+                                              None if dres is None else dres.contiguous()))
 
 
 def row_moments(x):

@@ -25,7 +25,7 @@ from ..global_vars import env
 from ..utils.common import seed
 from . import init
 from .common import get_tensor_parallel_mode
-from .functional import layer_norm, local_linear, masked_embedding
+from .functional import add_layer_norm, layer_norm, local_linear, masked_embedding
 from .layers_1d import (Classifier1D, Dropout1D, Embedding1D, LayerNorm1D, Linear1D, PatchEmbedding1D,
                         VocabParallelClassifier1D, VocabParallelEmbedding1D)
 from .layers_2d import (Classifier2D, Embedding2D, LayerNorm2D, Linear2D, PatchEmbedding2D,
@@ -140,7 +140,9 @@ class _PlainLayerNorm(nn.Module):
         self.bias = nn.Parameter(torch.zeros(normalized_shape))
         self.eps = eps
 
-    def forward(self, x):
+    def forward(self, x, residual=None):
+        if residual is not None:
+            return add_layer_norm(x, residual, self.weight, self.bias, self.eps)
         return layer_norm(x, self.weight, self.bias, self.eps)
 
 
@@ -166,10 +168,18 @@ class LayerNorm(nn.Module):
         mode = get_tensor_parallel_mode()
         norm = _PlainLayerNorm(normalized_shape, eps) if mode is None else \
             _parallel_layernorm[mode](normalized_shape, eps=eps, **_sp_kwargs(mode, sequence_parallel))
+        self._fused_residual = mode in (None, "1d")
         self.norm = _to(norm, dtype)
 
-    def forward(self, *args, **kwargs):
-        return self.norm(*args, **kwargs)
+    def forward(self, x, residual=None):
+        """``LN(x)``.  With ``residual`` the layer returns ``(x + residual, LN(x + residual))``: unsharded and 1D norms
+        compute both in one kernel, the 2D / 3D norms add first."""
+        if residual is None:
+            return self.norm(x)
+        if self._fused_residual:
+            return self.norm(x, residual)
+        total = x + residual
+        return total, self.norm(total)
 
     weight = property(lambda self: self.norm.weight)
     bias = property(lambda self: self.norm.bias)

@@ -38,8 +38,40 @@ class _LayerNorm(torch.autograd.Function):
         return dx, dg.to(ctx.p_dtype), db.to(ctx.p_dtype), None
 
 
+class _AddLayerNorm(torch.autograd.Function):
+    """``s = x + r`` and ``y = LN(s)`` in one pass; returns ``(s, y)``.  Backward: the gradient of ``s`` is the layer
+    norm's input gradient plus whatever reaches ``s`` directly (the residual path), again in one pass; ``x`` and ``r``
+    both receive it.  Replaces the separate residual add in front of every norm (benchmark/gpt2/gpt2.py:179-186)."""
+
+    @staticmethod
+    def forward(ctx, x, r, gamma, beta, eps):
+        cd = ops.compute_dtype(x)
+        x2 = as_compute(x.reshape(-1, x.shape[-1]), cd)
+        r2 = as_compute(r.reshape(-1, r.shape[-1]), cd)
+        y, mean, rstd, total = ops.layer_norm_fwd(x2, gamma, beta, eps, residual=r2)
+        ctx.save_for_backward(total, mean, rstd, gamma)
+        ctx.x_dtype, ctx.r_dtype, ctx.p_dtype = x.dtype, r.dtype, gamma.dtype
+        return total.view(x.shape), y.view(x.shape)
+
+    @staticmethod
+    def backward(ctx, ds, dy):
+        total, mean, rstd, gamma = ctx.saved_tensors
+        dy2 = as_compute(dy.reshape(-1, dy.shape[-1]), total.dtype)
+        ds2 = as_compute(ds.reshape(-1, ds.shape[-1]), total.dtype)
+        dx, dg, db = ops.layer_norm_bwd(dy2, total, mean, rstd, gamma, dres=ds2)
+        dx = dx.view(dy.shape)
+        gx = dx if dx.dtype == ctx.x_dtype else dx.to(ctx.x_dtype)
+        gr = dx if dx.dtype == ctx.r_dtype else dx.to(ctx.r_dtype)
+        return gx, gr, dg.to(ctx.p_dtype), db.to(ctx.p_dtype), None
+
+
 def layer_norm(x, gamma, beta, eps):
     return _LayerNorm.apply(x, gamma, beta, eps)
+
+
+def add_layer_norm(x, r, gamma, beta, eps):
+    """``(x + r, LN(x + r))``."""
+    return _AddLayerNorm.apply(x, r, gamma, beta, eps)
 
 
 class _MaskedEmbedding(torch.autograd.Function):

@@ -30,10 +30,10 @@ from ..utils.common import seed
 from . import init
 from .collective import broadcast
 from .common import set_tensor_parallel_attribute_by_partition as _stamp
-from .functional import layer_norm, masked_embedding
+from .functional import add_layer_norm, layer_norm, masked_embedding
 from .mesh import pm
 from .ops_1d import (gather_forward_split_backward, get_parallel_input, linear_1d, linear_1d_rows,
-                     mark_partial_grad, reduce_input, reduce_scatter_rows, set_parallel_input,
+                     mark_partial_grad, reduce_input, reduce_scatter_rows, set_parallel_input, skip_product,
                      split_forward_gather_backward)
 from .std import PatchEmbeddingSTD
 
@@ -115,10 +115,11 @@ class Linear1D_Row(nn.Module):
         if not self.parallel_input:
             x = split_forward_gather_backward(x, pm.PARALLEL_1D, dim=-1)
         b = None if self.skip_bias_add else self.bias
+        skip = skip_product(self)
         if self.sequence_parallel:      # the output keeps this rank's rows of the sum
-            y = linear_1d_rows(x, self.weight, b, pm.PARALLEL_1D, "scatter")
+            y = linear_1d_rows(x, self.weight, b, pm.PARALLEL_1D, "scatter", skip=skip)
         else:
-            y = linear_1d(x, self.weight, b, pm.PARALLEL_1D, reduce_fwd=True)
+            y = linear_1d(x, self.weight, b, pm.PARALLEL_1D, reduce_fwd=True, skip=skip)
         return (y, self.bias) if self.skip_bias_add else y
 
 
@@ -161,7 +162,10 @@ class LayerNorm1D(nn.Module):
             mark_partial_grad(self.weight)
             mark_partial_grad(self.bias)
 
-    def forward(self, x):
+    def forward(self, x, residual=None):
+        """``LN(x)``; with ``residual``: ``(x + residual, LN(x + residual))`` from one kernel."""
+        if residual is not None:
+            return add_layer_norm(x, residual, self.weight, self.bias, self.eps)
         return layer_norm(x, self.weight, self.bias, self.eps)
 
 

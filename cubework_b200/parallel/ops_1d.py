@@ -17,6 +17,24 @@ from . import fused
 from .collective import all_gather, all_reduce, reduce_scatter
 
 
+_RECOMPUTING = [0]
+
+
+class recomputing:
+    """Context in which a checkpointed block is re-run for its gradients (set by the models' checkpoint wrapper)."""
+
+    def __enter__(self):
+        _RECOMPUTING[0] += 1
+
+    def __exit__(self, *exc):
+        _RECOMPUTING[0] -= 1
+
+
+def skip_product(module) -> bool:
+    """True when ``module``'s output is not needed: it is the last linear of a block that is being re-run."""
+    return _RECOMPUTING[0] > 0 and getattr(module, "output_unused_in_recompute", False)
+
+
 def set_parallel_input(input_parallel: bool):
     env.parallel_input_1d = input_parallel
 
@@ -104,7 +122,7 @@ class _Linear1D(torch.autograd.Function):
     """
 
     @staticmethod
-    def forward(ctx, x, w, b, mode, reduce_fwd, reduce_bwd, act):
+    def forward(ctx, x, w, b, mode, reduce_fwd, reduce_bwd, act, skip=False):
         cd = ops.compute_dtype(x)
         x2 = x.reshape(-1, x.shape[-1])
         if x2.dtype != cd:
@@ -112,7 +130,10 @@ class _Linear1D(torch.autograd.Function):
         x2 = x2.contiguous()
         wc = ops.shadow(w, cd)
         z = None
-        if reduce_fwd and mode.world_size > 1:
+        if skip and act is None:
+            # re-run of a checkpointed block whose output nobody reads: the backward below needs x and w only
+            y = x2.new_empty((x2.shape[0], w.shape[0]))
+        elif reduce_fwd and mode.world_size > 1:
             assert act is None
             y = fused.gemm_all_reduce(x2, wc, False, True, mode, bias=b)
         elif act is not None:
@@ -159,11 +180,11 @@ class _Linear1D(torch.autograd.Function):
             dx = dx.view(ctx.x_shape)
             if dx.dtype != ctx.x_dtype:
                 dx = dx.to(ctx.x_dtype)
-        return dx, dw, db, None, None, None, None
+        return dx, dw, db, None, None, None, None, None
 
 
-def linear_1d(x, w, b, mode, reduce_fwd=False, reduce_bwd=False, act=None):
-    return _Linear1D.apply(x, w, b, mode, reduce_fwd, reduce_bwd, act)
+def linear_1d(x, w, b, mode, reduce_fwd=False, reduce_bwd=False, act=None, skip=False):
+    return _Linear1D.apply(x, w, b, mode, reduce_fwd, reduce_bwd, act, skip)
 
 
 class _Linear1DRows(torch.autograd.Function):
@@ -183,7 +204,7 @@ class _Linear1DRows(torch.autograd.Function):
     """
 
     @staticmethod
-    def forward(ctx, x, w, b, mode, kind, act):
+    def forward(ctx, x, w, b, mode, kind, act, skip=False):
         cd = ops.compute_dtype(x)
         x2 = x.reshape(-1, x.shape[-1])
         if x2.dtype != cd:
@@ -202,7 +223,10 @@ class _Linear1DRows(torch.autograd.Function):
             lead = (x.shape[0] * n, ) + tuple(x.shape[1:-1])
         else:
             assert act is None, "the activation belongs to the column-parallel linear of the pair"
-            y = fused.gather_gemm_reduce(x2, wc, False, True, scatter=(mode, 0), bias=b)
+            if skip:    # re-run of a checkpointed block whose output nobody reads (every rank skips alike)
+                y = x2.new_empty((x2.shape[0] // n, w.shape[0]))
+            else:
+                y = fused.gather_gemm_reduce(x2, wc, False, True, scatter=(mode, 0), bias=b)
             x_keep = x2
             assert x.shape[0] % n == 0, f"leading dimension {x.shape[0]} is not divisible by the group size {n}"
             lead = (x.shape[0] // n, ) + tuple(x.shape[1:-1])
@@ -250,14 +274,14 @@ class _Linear1DRows(torch.autograd.Function):
             dx = dx.view(ctx.x_shape)
             if dx.dtype != ctx.x_dtype:
                 dx = dx.to(ctx.x_dtype)
-        return dx, dw, db, None, None, None
+        return dx, dw, db, None, None, None, None
 
 
-def linear_1d_rows(x, w, b, mode, kind, act=None):
+def linear_1d_rows(x, w, b, mode, kind, act=None, skip=False):
     """See :class:`_Linear1DRows`; with a group of one this is the plain linear."""
     if mode.world_size == 1:
-        return _Linear1D.apply(x, w, b, mode, False, False, act)
-    return _Linear1DRows.apply(x, w, b, mode, kind, act)
+        return _Linear1D.apply(x, w, b, mode, False, False, act, skip)
+    return _Linear1DRows.apply(x, w, b, mode, kind, act, skip)
 
 
 class _ScatterRows(torch.autograd.Function):

@@ -162,6 +162,8 @@ def _push_ctas(push_bytes, M, N, K, n):
     in flight).  The GEMM CTAs start with the tiles that need no remote data (1/n of the work) and then follow
     the arrival order, so the shards should be out within the remaining (n-1)/n of the product's time; more than
     the links carry (about 750 GB/s) is pointless, and every communication CTA is an SM the GEMM loses."""
+    if push_bytes == 0 or n < 2:
+        return 1          # nothing is gathered: the kernel launches no communication CTA
     if _PUSH_CTAS > 0:
         return _PUSH_CTAS
     t_gemm = max(2.0 * M * N * K / 1.2e15, 20e-6)

@@ -126,6 +126,32 @@ def test_layer_norm(H):
     assert _rel_err(dx2, xr.grad) < 6e-3 and _rel_err(dg2, gr.grad) < 1e-3 and _rel_err(db2, br.grad) < 1e-3
 
 
+@pytest.mark.parametrize("H", [64, 1600, 2048, 5120])
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+def test_add_layer_norm_fused(H, dtype):
+    """Residual add + layer norm in one kernel (forward: the sum and its normalised value; backward: the norm's input
+    gradient plus the gradient that reaches the sum directly) against the fp32 formulation."""
+    ops, ext = _ops()
+    from cubework_b200.parallel.functional import add_layer_norm
+    torch.manual_seed(6)
+    rows = 391
+    x = (torch.randn(rows, H, device=DEV) * 1.5).to(dtype).requires_grad_(True)
+    r = (torch.randn(rows, H, device=DEV) * 0.5 + 0.3).to(dtype).requires_grad_(True)
+    g = torch.randn(H, device=DEV).requires_grad_(True)
+    b = torch.randn(H, device=DEV).requires_grad_(True)
+    ds, dy = torch.randn(rows, H, device=DEV).to(dtype), torch.randn(rows, H, device=DEV).to(dtype)
+    total, y = add_layer_norm(x, r, g, b, 1e-5)
+    torch.autograd.backward([total, y], [ds, dy])
+    xr, rr = x.detach().float().requires_grad_(True), r.detach().float().requires_grad_(True)
+    gr, br = g.detach().clone().requires_grad_(True), b.detach().clone().requires_grad_(True)
+    tr = (xr + rr).to(dtype).float() + (xr + rr - (xr + rr).detach())      # the kernel normalises the rounded sum
+    yr = torch.nn.functional.layer_norm(tr, (H, ), gr, br, 1e-5)
+    torch.autograd.backward([tr, yr], [ds.float(), dy.float()])
+    assert _rel_err(total, tr) < 1e-3 and _rel_err(y, yr) < 6e-3
+    assert _rel_err(x.grad, xr.grad) < 8e-3 and torch.equal(x.grad, r.grad)
+    assert _rel_err(g.grad, gr.grad) < 2e-3 and _rel_err(b.grad, br.grad) < 2e-3
+
+
 @pytest.mark.parametrize("V,start", [(6288, 0), (1000, 3000), (50304, 0)])
 def test_cross_entropy_pieces(V, start):
     ops, ext = _ops()

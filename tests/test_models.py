@@ -137,3 +137,39 @@ def test_gpt2_tiny_sequence_parallel_matches_unsharded(world):
 def test_gpt2_tiny_tp_times_dp():
     """tp=2 x dp=2: replicas see the same batch here, so the result still equals the unsharded model."""
     run_dist(_check_family, 4, tp="1d", tp_size=2, args=("gpt2", 1e-5))
+
+
+def _check_checkpointed(family, sp):
+    """Activation checkpointing (with dropout, i.e. with random streams to rewind, and with the skipped last
+    product of every re-run block) gives the gradients of the plain model."""
+    import cubework_b200 as cube  # noqa: F401
+    from cubework_b200.models import gpt2
+    from cubework_b200.parallel.ops_1d import reduce_partial_grads
+    from cubework_b200.utils import checkpoint as ck
+
+    def build(ckpt):
+        torch.manual_seed(11)
+        return gpt2.build_model("gpt2_tiny", 64, dropout=0.1, embedding_dropout=0.1, checkpoint=ckpt, sequence_parallel=sp)
+
+    ref, model = build(False), build(True)
+    model.load_state_dict(ref.state_dict())
+    crit = gpt2.GPT2LMLoss()
+    batch = _batch("gpt2")
+    grads = []
+    for m in (ref, model):
+        m.train()
+        saved = ck._rng_states()
+        torch.manual_seed(77)
+        loss = crit(m(batch["input_ids"], batch["attention_mask"]), batch["labels"])
+        loss.backward()
+        reduce_partial_grads(list(m.parameters()))
+        ck._set_rng_states(saved)            # both runs start from the same random streams
+        grads.append((loss.item(), {k: p.grad.clone() for k, p in m.named_parameters()}))
+    assert abs(grads[0][0] - grads[1][0]) < 1e-6
+    for k in grads[0][1]:
+        assert torch.allclose(grads[0][1][k], grads[1][1][k], rtol=1e-4, atol=1e-6), k
+
+
+@pytest.mark.parametrize("sp", [False, True])
+def test_gpt2_activation_checkpointing_matches_plain(sp):
+    run_dist(_check_checkpointed, 2, tp="1d", tp_size=2, args=("gpt2", sp))
