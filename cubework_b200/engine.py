@@ -111,7 +111,7 @@ class Trainer:
             total = loss.detach() if total is None else total + loss.detach()
         if tm is not None:
             tm.start("opt")
-        _sync_async_grads()
+        _sync_async_grads(host_sync=False)
         if self._partial_params:
             reduce_partial_grads(self._partial_params)
         if self.scaler is not None:

@@ -96,10 +96,15 @@ def register_async_grad_hook(param):
     param.register_hook(_hook)
 
 
-def synchronize(params=()):
-    """Wait for every outstanding asynchronous parameter-gradient reduction."""
+def synchronize(params=(), host_sync=True):
+    """Wait for every outstanding asynchronous parameter-gradient reduction.
+
+    The reductions are awaited on the current stream (``work.wait()`` orders the stream behind the collective, it does
+    not block the host).  ``host_sync`` additionally blocks the host until the stream has drained, which is what a
+    caller that is about to read gradients on the host wants (the reference's ``synchronize``, module/utils.py:88-92);
+    the training engine passes ``False`` so that the host keeps running ahead of the device."""
     _bucket.synchronize(params)
-    if torch.cuda.is_available():
+    if host_sync and torch.cuda.is_available():
         torch.cuda.current_stream().synchronize()
     if len(_bucket) > 0:
         raise RuntimeError(f"{len(_bucket)} asynchronous gradient(s) not collected.")
