@@ -153,6 +153,24 @@ def run_ours(args):
     host_batches = _synthetic_batches(torch, 4, GLOBAL_BATCH)
     dev_batches = [{k: v.to(dev) for k, v in b.items()} for b in host_batches]
 
+    # First step: every rank checks the kernels' status word; if any rank saw a bounded wait expire (a peer that
+    # did not show up in a fused exchange) all ranks switch to the unfused composition (own GEMM + NCCL) together
+    # and say so in the printed line, instead of measuring a broken run.
+    from cubework_b200.parallel import symm
+    fused_error = None
+    trainer.step(dev_batches[0])
+    torch.cuda.synchronize()
+    try:
+        ext.check_status()
+        bad = 0
+    except RuntimeError as e:
+        bad, fused_error = 1, str(e)
+    flag = torch.tensor([bad], device=dev)
+    dist.all_reduce(flag, op=dist.ReduceOp.MAX)
+    if flag.item():
+        fused_error = fused_error or "a peer reported a device-side timeout"
+        symm._DISABLED = True
+        symm.invalidate_all()
     for i in range(args.warmup):
         trainer.step(dev_batches[i % len(dev_batches)])
     torch.cuda.synchronize()
@@ -207,6 +225,8 @@ def run_ours(args):
                     "last_loss": losses[-1]},
             "gpu_launches": launches,
             "sequence_parallel": n > 1,
+            "fused_kernels": fused_error is None,
+            **({"fused_error": fused_error} if fused_error else {}),
             "fused_per_step": fused,
             "nccl_per_step": nccl,
             "extra": {"activation_checkpointing_off": {"value": tokens / (nockpt_ms / 1e3), "unit": "tokens/s",

@@ -5,9 +5,14 @@
     torchrun --nproc_per_node 8 benchmark/linear/bench_linear.py --tp 3d --tp_size 8
 
 ``X[M=16384, K] x W[K, N]`` with ``K = N`` in {4096, 8192, 12288}, bf16, X and W ~ N(0,1).  For each size the
-script times fwd+bwd (CUDA events, max over ranks) twice: with the fused kernels, and with the cuBLAS + NCCL
-composition the reference uses (``CUBEWORK_B200_KERNELS=0``-style path is selected per call).  It prints ms and
-the achieved fraction of the roofline ``max(FLOPs / GEMM peak, NVLink bytes / link bandwidth)``.
+script times fwd+bwd (CUDA events, max over ranks) three times: with the fused kernels, with this package's GEMM
+followed by NCCL, and with cuBLAS + NCCL through the same layer code (``CUBEWORK_B200_KERNELS=0``).  It prints ms
+and the achieved fraction of the roofline ``max(FLOPs / GEMM peak, NVLink bytes / link bandwidth)``.
+
+``--impl reference`` times the unmodified reference instead (``cubework.module.Linear`` from ``baseline/_ref`` under
+its fp16 autocast, i.e. its own NCCL + cuBLAS path: q rounds of broadcast + addmm in 2D, all-gather / matmul /
+reduce-scatter in 3D, parallel_2d/_operation.py:15-239, parallel_3d/_operation.py:12-68) on the same shapes and
+with the same timing, and prints the same JSON lines.
 """
 import argparse
 import json
@@ -94,10 +99,74 @@ def time_fb(layer, x, iters=10, warm=3):
     return ms.item()
 
 
+def run_reference(args):
+    """The reference's ``cubework.module.Linear`` in the requested mode (flags are read from ``sys.argv`` by its own
+    ``initialize_distributed``)."""
+    import math
+    import types
+    root = os.path.join(os.path.dirname(os.path.abspath(__file__)), "..", "..", "baseline", "_ref")
+    six = types.ModuleType("torch._six")      # removed in torch 2.x; cubework/utils/clip_grad.py imports `inf` from it
+    six.inf = math.inf
+    sys.modules["torch._six"] = six
+    sys.path.insert(0, root)
+    import cubework
+    import cubework.module as ref_nn
+    from cubework.distributed import ParallelManager as rpm
+    from cubework.global_vars import env as renv
+    sys.argv = [sys.argv[0], "--tp", args.tensor_parallel, "--tp_size", str(args.tensor_parallel_size)]
+    cubework.initialize_distributed()
+    dev = torch.device("cuda", torch.cuda.current_device())
+    mode, tp = args.tensor_parallel, rpm.TENSOR.world_size
+    peak, src = peaks()
+    for K in args.sizes:
+        N = K
+        if mode == "1d":
+            renv.parallel_input_1d = args.kind == "row"
+        layer = ref_nn.Linear(K, N).to(dev)
+        if mode == "1d":
+            x = torch.randn(M, K // tp if args.kind == "row" else K, device=dev)
+        elif mode == "2d":
+            x = torch.randn(M // renv.summa_dim, K // renv.summa_dim, device=dev)
+        else:
+            x = torch.randn(M // renv.depth_3d**2, K // renv.depth_3d, device=dev)
+
+        def once():
+            xi = x.detach().requires_grad_(True)
+            with torch.cuda.amp.autocast(enabled=True):
+                y = layer(xi)
+            y.backward(torch.ones_like(y))
+            layer.zero_grad(set_to_none=True)
+
+        for _ in range(3):
+            once()
+        dist.barrier()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(10):
+            once()
+        e1.record()
+        torch.cuda.synchronize()
+        ms = torch.tensor([e0.elapsed_time(e1) / 10], device=dev)
+        dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+        if dist.get_rank() == 0:
+            print(json.dumps({"impl": "reference", "layout": mode + ("-" + args.kind if mode == "1d" else ""), "tp": tp,
+                              "M": M, "K": K, "N": N, "ms": {"reference (fp16 autocast)": round(ms.item(), 4)}}), flush=True)
+        del layer
+    cubework.destroy_distributed()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--kind", choices=["col", "row"], default="row")
     ap.add_argument("--sizes", type=int, nargs="*", default=[4096, 8192, 12288])
+    ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
+    if "--impl" in sys.argv and sys.argv[sys.argv.index("--impl") + 1] == "reference":
+        ap.add_argument("--tensor_parallel", "--tp", default="1d")
+        ap.add_argument("--tensor_parallel_size", "--tp_size", type=int, default=1)
+        ap.add_argument("--backend", default="nccl")
+        ap.add_argument("--seed", type=int, default=None)
+        return run_reference(ap.parse_args())
     args = cube.initialize_distributed(ap)
     dev = torch.device("cuda", torch.cuda.current_device())
     mode, tp = env.mode, pm.TENSOR.world_size

@@ -8,6 +8,7 @@ two weight-gradient products (both operands MN-major, fp32 output, split-K), and
 call, median of 10 after 3 warm-ups, a 256 MB scratch write between calls (larger than L2).  The cuBLAS column runs
 the same contraction with a 16-bit output; for the GELU row it adds ``torch.nn.functional.gelu`` on the result.
 """
+import argparse
 import os
 import sys
 
@@ -18,6 +19,11 @@ import torch.nn.functional as F  # noqa: E402
 
 from cubework_b200.ops import ext  # noqa: E402
 
+ap = argparse.ArgumentParser()
+ap.add_argument("--only", default=None, help="run only the cases whose name contains this text (for profiler captures)")
+ap.add_argument("--iters", type=int, default=10)
+ap.add_argument("--no-library", action="store_true", help="skip the cuBLAS column")
+cli = ap.parse_args()
 ext.require()
 BF = torch.bfloat16
 T = 32768
@@ -40,7 +46,7 @@ def timed(f):
     for _ in range(3):
         f()
     ts = []
-    for _ in range(10):
+    for _ in range(cli.iters):
         flush.add_(1)
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record()
@@ -52,6 +58,8 @@ def timed(f):
 
 
 for name, sa, sb, ta, tb, act, f32 in CASES:
+    if cli.only and cli.only not in name:
+        continue
     a = torch.randn(*sa, device="cuda", dtype=BF)
     b = torch.randn(*sb, device="cuda", dtype=BF)
     M, K = (sa[1], sa[0]) if ta else sa
@@ -70,7 +78,8 @@ for name, sa, sb, ta, tb, act, f32 in CASES:
             return F.gelu(z), z
         return A @ Bm
 
-    t_own, t_lib = timed(ours), timed(lib)
+    t_own = timed(ours)
+    t_lib = t_own if cli.no_library else timed(lib)
     fl = 2.0 * M * N * K
     print(f"{name}: tcgen05 {t_own:.3f} ms {fl / t_own / 1e9:7.1f} TFLOP/s | cuBLAS {t_lib:.3f} ms {fl / t_lib / 1e9:7.1f} TFLOP/s"
           f" | ratio {t_lib / t_own:.3f}", flush=True)

@@ -44,7 +44,9 @@ extern "C" {
 #define CW_NOALLOC_OK 0
 #define CW_NOALLOC_ERR_TOO_LARGE 1  /* hidden > CW_NOALLOC_MAX_HIDDEN */
 #define CW_NOALLOC_ERR_BAD_ARGUMENT 2 /* null pointer, rows < 1, hidden not a multiple of 8, misaligned tensor */
-#define CW_NOALLOC_ERR_CUDA 3       /* symbol look-up or kernel launch failed; see cudaGetLastError() */
+#define CW_NOALLOC_ERR_CUDA 3       /* symbol look-up or kernel launch failed; see cudaGetLastError().  The launches
+                                      are checked with cudaPeekAtLastError(), so an error that the calling thread
+                                      left pending from earlier work of its own is reported here as well */
 
 int cw_layer_norm_bwd_noalloc(const void* dy, const void* x, const float* mean, const float* rstd, const float* gamma,
                               void* dx, float* dgamma, float* dbeta, int rows, int hidden, int is_bf16,

@@ -144,7 +144,8 @@ def test_add_layer_norm_fused(H, dtype):
     torch.autograd.backward([total, y], [ds, dy])
     xr, rr = x.detach().float().requires_grad_(True), r.detach().float().requires_grad_(True)
     gr, br = g.detach().clone().requires_grad_(True), b.detach().clone().requires_grad_(True)
-    tr = (xr + rr).to(dtype).float() + (xr + rr - (xr + rr).detach())      # the kernel normalises the rounded sum
+    sr = xr + rr
+    tr = sr + (sr.to(dtype).float() - sr).detach()       # the kernel normalises the rounded sum
     yr = torch.nn.functional.layer_norm(tr, (H, ), gr, br, 1e-5)
     torch.autograd.backward([tr, yr], [ds.float(), dy.float()])
     assert _rel_err(total, tr) < 1e-3 and _rel_err(y, yr) < 6e-3

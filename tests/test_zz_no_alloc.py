@@ -23,9 +23,7 @@ MAX_HIDDEN = 8192
 
 def _lib():
     from cubework_b200.ops import build
-    path = build.noalloc_so_path()
-    if not os.path.exists(path):
-        build.build_noalloc()
+    path = build.build_noalloc()       # rebuilds only when the source or the header is newer than the library
     lib = ctypes.CDLL(path)
     fn = lib.cw_layer_norm_bwd_noalloc
     fn.restype = ctypes.c_int
