@@ -44,6 +44,11 @@ ACTIVATION_CHECKPOINTING = True   # one value for both arms (see the module docs
 BASELINE_PUBLISHED = None   # the reference publishes no number for this (or any) configuration
 
 
+def _model_name():
+    h = MODEL["num_heads"]
+    return f"GPT-2 XL-shape (48L, hidden 1600, {h} heads x {MODEL['hidden_size'] // h}, MLP 6400, vocab 50304)"
+
+
 def _env_defaults(n):
     os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
     if "RANK" not in os.environ:
@@ -215,7 +220,7 @@ def run_ours(args):
             "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "strong",
             "vs_baseline": (value / BASELINE_PUBLISHED) if BASELINE_PUBLISHED else None, "dtype": "bf16",
             "data": "synthetic token ids (uniform), random-init weights N(0,0.02)", "impl": "ours",
-            "config": {"model": "GPT-2 XL-shape (48L, hidden 1600, 64 heads x 25, MLP 6400, vocab 50304)",
+            "config": {"model": _model_name(),
                        "global_batch": GLOBAL_BATCH, "seq_len": SEQ, "parallelism": f"tp{n} (1D)",
                        "optimizer": "AdamW + clip 1.0", "activation_checkpointing": ACTIVATION_CHECKPOINTING,
                        "l2": "working set >> L2 (126 MB); no flush between steps"},
@@ -319,7 +324,7 @@ def run_reference(args):
             "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "strong",
             "vs_baseline": None, "dtype": "fp16 autocast + GradScaler (the reference's ops cast to fp16 themselves)",
             "data": "synthetic token ids (uniform), random-init weights N(0,0.02)", "impl": "reference",
-            "config": {"model": "GPT-2 XL-shape (48L, hidden 1600, 64 heads x 25, MLP 6400, vocab 50304)",
+            "config": {"model": _model_name(),
                        "global_batch": GLOBAL_BATCH, "seq_len": SEQ, "parallelism": f"tp{n} (1D)",
                        "optimizer": "AdamW + clip 1.0", "activation_checkpointing": ACTIVATION_CHECKPOINTING,
                        "l2": "working set >> L2 (126 MB); no flush between steps"},
@@ -337,7 +342,11 @@ def main():
     ap.add_argument("--steps", type=int, default=8)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
+    ap.add_argument("--heads", type=int, default=MODEL["num_heads"],
+                    help="attention heads (default 64 x 25, the reference's gpt2_xl preset; 25 gives 25 x 64, which "
+                         "only 1-GPU runs can use: 25 heads do not divide over 2, 4 or 8 ranks)")
     args = ap.parse_args()
+    MODEL["num_heads"] = args.heads
     args.warmup = max(args.warmup, 3)
     _env_defaults(args.gpus)
     if args.impl == "reference":
