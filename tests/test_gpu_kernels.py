@@ -272,6 +272,36 @@ def test_attention_matches_reference(causal, dh, T):
     assert _rel_err(qkv.grad, q32.grad) < 2e-2
 
 
+@pytest.mark.parametrize("dh,heads,batch", [(25, 64, 8), (64, 25, 8), (64, 16, 32)])
+def test_attention_benchmark_regime_causal_with_key_bias(dh, heads, batch):
+    """The benchmark's regime: sequence 1024, enough (batch x heads) tiles that every persistent CTA of the forward
+    runs several tiles (512 / 200 / 512 (batch, head) pairs x 8 query tiles on 148 SMs), causal masking AND a
+    non-zero key bias (padding) together, as GPT-2 passes them; forward and backward against the fp32 formulation."""
+    ops, ext = _ops()
+    torch.manual_seed(9)
+    T = 1024
+    qkv = (torch.randn(batch, T, heads, 3 * dh, device=DEV) * 0.5).bfloat16().requires_grad_(True)
+    key_bias = torch.zeros(batch, T, device=DEV)
+    key_bias[0, T - 100:] = -10000.0            # right padding of different lengths
+    key_bias[1, T - 1:] = -10000.0
+    key_bias[batch - 1, 517:] = -10000.0
+    out = ops.attention_packed(qkv, True, key_bias)
+    dout = torch.randn_like(out)
+    out.backward(dout)
+    ext.check_status()
+    # the fp32 oracle one batch entry at a time (its scores are [heads, T, T] floats)
+    worst_o = worst_g = 0.0
+    for b in (0, 1, batch // 2, batch - 1):
+        q32 = qkv[b:b + 1].detach().float().requires_grad_(True)
+        q, k, v = q32.permute(0, 2, 1, 3).chunk(3, dim=-1)
+        ref = ops.attention_reference(q, k, v, True, key_bias[b:b + 1]).transpose(1, 2).reshape(1, T, heads * dh)
+        ref.backward(dout[b:b + 1].float())
+        # rows of padded queries attend to real keys only; compare everything
+        worst_o = max(worst_o, _rel_err(out[b:b + 1], ref))
+        worst_g = max(worst_g, _rel_err(qkv.grad[b:b + 1], q32.grad))
+    assert worst_o < 1e-2 and worst_g < 2e-2, (worst_o, worst_g)
+
+
 def test_gpt2_tiny_bf16_step_close_to_fp32_cpu():
     """The whole bf16 kernel path (GEMM epilogues, layer norm, attention, CE, AdamW) on a tiny GPT-2."""
     ops, ext = _ops()
