@@ -3,8 +3,10 @@
     torchrun --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 benchmark/linear/sp_linear_bench.py [--trace]
 
 For the forward and backward products of the attention / MLP linears (32768 tokens, hidden 1600, MLP 6400, split N
-ways) the script times three things with CUDA events (median of 8 calls after 3 warm-ups, a 200 MB scratch write and
-a barrier before every call, maximum over ranks): the plain tcgen05 GEMM of the same per-rank shape (no exchange),
+ways) the script times three things with CUDA events (median of 8 samples after 3 warm-ups; a sample is four
+back-to-back calls, so that the host's launch latency hides behind the previous call as it does in a training step,
+after a 200 MB scratch write and a barrier; operands and results of one call exceed L2; maximum over ranks): the
+plain tcgen05 GEMM of the same per-rank shape (no exchange),
 the fused all-gather -> GEMM or GEMM -> reduce-scatter kernel, and the link floor (bytes every GPU has to send,
 (N-1)/N of the 105 MB activation, at the measured 770 GB/s peer-copy rate).  The roofline of a fused product is the
 larger of the plain GEMM time at the measured GEMM peak and the link floor.
@@ -42,7 +44,7 @@ def peak_tflops():
         return 1590.0, "fallback"
 
 
-def timed(fn, flush, dev, iters=8):
+def timed(fn, flush, dev, iters=8, reps=4):
     for _ in range(3):
         fn()
     torch.cuda.synchronize()
@@ -53,10 +55,11 @@ def timed(fn, flush, dev, iters=8):
         dist.barrier()
         s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         s.record()
-        fn()
+        for _ in range(reps):
+            fn()
         e.record()
         torch.cuda.synchronize()
-        ts.append(s.elapsed_time(e))
+        ts.append(s.elapsed_time(e) / reps)
     t = torch.tensor(sorted(ts)[len(ts) // 2], device=dev)
     dist.all_reduce(t, op=dist.ReduceOp.MAX)
     return t.item() * 1e3

@@ -159,16 +159,16 @@ def _plan_gather(t, spec, mn_major):
 
 def _push_ctas(push_bytes, M, N, K, n):
     """Communication CTAs for the operand gathers of one call.  One CTA moves about 40 GB/s (32 KB pieces, a dozen
-    in flight).  The GEMM CTAs start with the tiles that need no remote data (1/n of the work) and then follow
-    the arrival order, so the shards should be out within the remaining (n-1)/n of the product's time; more than
-    the links carry (about 750 GB/s) is pointless, and every communication CTA is an SM the GEMM loses."""
+    in flight), the links carry about 750 GB/s per direction, and every communication CTA is an SM the GEMM loses.
+    Sixteen saturate a link between two GPUs (measured: 671 GB/s) and get a shard across before the tiles that
+    need it first come up in every layout tried; fewer (sized to the product's duration) starved the layouts whose
+    first tiles already read remote data (SUMMA ``ABT`` / ``ATB``: 2.09 / 2.76 ms against 1.84 / 2.38 ms).  With four
+    or more sources all links are busy at once and twenty are used."""
     if push_bytes == 0 or n < 2:
         return 1          # nothing is gathered: the kernel launches no communication CTA
     if _PUSH_CTAS > 0:
         return _PUSH_CTAS
-    t_gemm = max(2.0 * M * N * K / 1.2e15, 20e-6)
-    rate = min(push_bytes / (0.8 * t_gemm * (n - 1) / n), 750e9)
-    return int(min(20, max(4, -(-rate // 40e9))))
+    return 16 if n < 4 else 20
 
 
 def _aligned(t):
