@@ -37,6 +37,7 @@ class Trainer:
         self.steps = 0
         # replicated parameters applied to row-sharded activations (1D sequence_parallel): summed over the group
         self._partial_params = [p for p in model.parameters() if getattr(p, PARTIAL_GRAD, False)]
+        self._params = list(model.parameters())      # walking the module tree every step costs host milliseconds
         self.status_interval = 16     # steps between reads of the kernels' host-mapped error word
 
     @staticmethod
@@ -117,7 +118,7 @@ class Trainer:
         if self.scaler is not None:
             self.scaler.unscale_(self.optimizer)
         if self.clip is not None and self.clip > 0:
-            clip_grad_norm(self.model.parameters(), self.clip)
+            clip_grad_norm(self._params, self.clip)
         if self.scaler is not None:
             self.scaler.step(self.optimizer)
             self.scaler.update()

@@ -897,6 +897,10 @@ static void launch_ggs(const CUtensorMap& ta, const CUtensorMap& tb, const CUten
     C10_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kGgsSmemBytes));
     configured = true;
   }
+  // Co-residency: GEMM CTAs spin (bounded) on flags that the communication CTAs of the peers' launches write, and
+  // the peers' GEMM CTAs on this launch's.  The grid is exactly one CTA per SM and every CTA takes the SM's whole
+  // shared memory, so all CTAs are resident at once as long as no other kernel holds SMs while this one starts; a
+  // concurrent kernel on another stream turns into a stall that the bounded waits report through the status word.
   kern<<<p.num_gemm_ctas + p.num_comm_ctas, kGgsThreads, kGgsSmemBytes, stream>>>(ta, tb, tao, tbo, to, tz, p);
   C10_CUDA_KERNEL_LAUNCH_CHECK();
 }

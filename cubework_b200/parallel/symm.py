@@ -49,11 +49,17 @@ def prefer_fused_gather_scatter(M, N, K) -> bool:
 _GGS_MIN_FLOPS = float(os.environ.get("CUBEWORK_B200_FUSED_MIN_GFLOP", "20")) * 1e9
 
 
+_HAS_FUSED = None
+
+
 def available() -> bool:
-    if _DISABLED or not torch.cuda.is_available():
+    global _HAS_FUSED
+    if _DISABLED:
         return False
-    from ..ops import ext
-    return ext.has("fused")
+    if _HAS_FUSED is None:
+        from ..ops import ext
+        _HAS_FUSED = torch.cuda.is_available() and ext.has("fused")
+    return _HAS_FUSED
 
 
 def release_all():

@@ -62,6 +62,17 @@ class Workspace:
         dist.barrier(group=self.mode.cpu_group)
         return peers
 
+    def halves(self, name, half_bytes):
+        """Every rank's pointers to the two halves of a double-buffered region (cached lists: this is on the path
+        of every fused call)."""
+        key = name + "/halves"
+        both = self.ptrs.get(key)
+        if both is None:
+            base = self.region(name, 2 * half_bytes)
+            both = ([p for p in base], [p + half_bytes for p in base])
+            self.ptrs[key] = both
+        return both
+
     def all_reduce_regions(self):
         flag_bytes = 4 * (_DONE_CAP * 8 + self.owned_cap * self.n * 8)
         return (self.region("stage", _STAGE_BYTES), self.region("result", _RESULT_BYTES),
@@ -239,20 +250,17 @@ def fused_gather_gemm_scatter(a, b, trans_a, trans_b, gather_a, gather_b, scatte
         if plan is None:
             return [], [], []
         ws = spaces[spec[0].name]
-        bufs = ws.region(role, 2 * _GATHER_HALF)
+        bufs = ws.halves(role, _GATHER_HALF)[ws.epoch & 1]
         flags = ws.region(role + "_flags", 4 * 8 * _MAX_PANELS, True)
-        half = (ws.epoch & 1) * _GATHER_HALF
-        return [plan[0], ws.me, plan[1], plan[2], ws.epoch], [p + half for p in bufs], flags
+        return [plan[0], ws.me, plan[1], plan[2], ws.epoch], bufs, flags
 
     ga_cfg, ga_bufs, ga_flags = gather_args(ga, gather_a, "ga")
     gb_cfg, gb_bufs, gb_flags = gather_args(gb, gather_b, "gb")
     sc_cfg, sc_stage, sc_flags = [], [], []
     if sc is not None:
         ws = spaces[sc[0].name]
-        stage = ws.region("rs_stage", 2 * _RS_HALF)
+        sc_stage = ws.halves("rs_stage", _RS_HALF)[ws.epoch & 1]
         sc_flags = ws.region("rs_flags", 4 * 8 * (_RS_HALF // TILE_BYTES), True)
-        half = (ws.epoch & 1) * _RS_HALF
-        sc_stage = [p + half for p in stage]
         sc_cfg = [sc[1], sc[2], ws.me, ws.epoch]
     out = torch.empty((Ms, Ns), dtype=out_dtype, device=a.device)
     z = torch.empty((Ms, Ns), dtype=a.dtype, device=a.device) if pre_act_out else None
