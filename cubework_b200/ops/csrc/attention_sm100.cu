@@ -90,7 +90,9 @@ struct AttnParams {
   const float* delta;   // [B, H, T]  rowsum(dO * O)
   float* dq_acc;        // [B, H, T, DP] fp32 scratch, zero-initialised (DP = padded head dim)
   void* dqkv;           // [B, T, H, 3*dh]
-  long long* trace;     // optional [2][4096][2]: (event, globaltimer) stamps of CTA 0 (row 0: softmax group 0, row 1: MMA issuer)
+  int* work_counter;    // zero-initialised: next work item of the persistent backward
+  long long* trace;     // optional [3][4096][2]: (event, globaltimer) stamps of CTA 0 (row 0: softmax group 0 / compute thread 0,
+                        // row 1: MMA issuer); the persistent backward adds per-CTA totals in row 2
 };
 __device__ __forceinline__ void attn_trace(long long* trace, int row, int& n, int code) {
   if (trace != nullptr && blockIdx.x == 0 && n < 4096) {
@@ -995,6 +997,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
   bool ok = true;
   int it = 0, ntr = 0;
   const bool trb = tid == 0 && blockIdx.y == 0 && blockIdx.z == 0;
+  if (trb) attn_trace(p.trace, 0, ntr, 0);
   if (kSep && tid == 0 && i0 < n_q) issue_scores(0, 0);
   for (int i = i0; i < n_q && ok; ++i, ++it) {
     const int q0 = i * kBlk;
@@ -1171,8 +1174,10 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
       }
     }
   }
+  if (trb) attn_trace(p.trace, 0, ntr, 8);
   if (tid == 0) bulk_wait_group0();
   __syncthreads();          // the last reduction has read its staging area, which the rows below may reuse
+  if (trb) attn_trace(p.trace, 0, ntr, 9);
 
   if (ok && it > 0) {
     // dK (threads of half 0) and dV (half 1): rows go through shared memory (P / dS are free now) so that each global
@@ -1220,9 +1225,524 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
   }
   tc_fence_before();
   __syncthreads();
+  if (trb) attn_trace(p.trace, 0, ntr, 10);
   if (warp == 0) {
     tc_fence_after();
     tmem_dealloc(tmem, kTmemCols);
+  }
+}
+
+// P and dS of 16 scores of a row as packed 16-bit pairs, kept in registers: p = exp2(s*sc2 + bias - lse),
+// ds = p * (dp - delta) * scale.  `pk` / `dk` point at the 8 words of this half of the thread's chunk.
+template <bool MASKED, bool BIAS, typename T>
+__device__ __forceinline__ void bwd_half_regs(const uint32_t (&rs)[16], const uint32_t (&rp)[16], const float* bias, float sc2,
+                                              float lse2, float scale, float nds, int key0, int q_idx, int Tn, bool causal,
+                                              uint32_t* pk, uint32_t* dk) {
+#pragma unroll
+  for (int q = 0; q < 4; ++q) {
+    float bv[4] = {0.f, 0.f, 0.f, 0.f};
+    if (BIAS) {
+      const float4 t = reinterpret_cast<const float4*>(bias)[q];    // a broadcast load: all lanes read the same keys
+      bv[0] = t.x; bv[1] = t.y; bv[2] = t.z; bv[3] = t.w;
+    }
+    float pr[4], ds[4];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const int e = 4 * q + u;
+      float v = ex2_approx(fmaf(__uint_as_float(rs[e]), sc2, BIAS ? bv[u] - lse2 : -lse2));
+      if (MASKED) {
+        const int key = key0 + e;
+        if (key >= Tn || q_idx >= Tn || (causal && key > q_idx)) v = 0.f;
+      }
+      pr[u] = v;
+      ds[u] = v * fmaf(__uint_as_float(rp[e]), scale, nds);
+    }
+    pk[2 * q] = pack_pair<T>(pr[0], pr[1]);
+    pk[2 * q + 1] = pack_pair<T>(pr[2], pr[3]);
+    dk[2 * q] = pack_pair<T>(ds[0], ds[1]);
+    dk[2 * q + 1] = pack_pair<T>(ds[2], ds[3]);
+  }
+}
+// Write 32 consecutive columns [c0, c0+32) of row r of a [128 x 128] 16-bit image from packed pairs.
+__device__ __forceinline__ void store_packed_chunk(uint8_t* img, int r, int c0, const uint32_t (&pk)[16]) {
+#pragma unroll
+  for (int q = 0; q < 4; ++q)
+    *reinterpret_cast<uint4*>(img + img_off(r, c0 + q * 8)) = make_uint4(pk[4 * q], pk[4 * q + 1], pk[4 * q + 2], pk[4 * q + 3]);
+}
+
+// ------------------------------------------------------------------------------------------------
+// Backward for head dims up to 64: persistent, warp-specialised.  Sixteen compute warps (four threads per query row,
+// one per 32-key chunk: four warps per scheduler cover each other's TMEM and exponential latencies), two MMA-issuing
+// warps and one TMA warp per CTA; CTAs take (key block, head, batch) work items from a global counter in
+// (batch, head)-major order, so the key blocks that add into the same dQ rows run at about the same time and the
+// fp32 accumulator stays in L2.  Per (query block, key block) pair nobody meets at a CTA-wide barrier:
+//   MMA warp A:  S_{i+1}, dP_{i+1} are issued as soon as the compute warps have read S_i, dP_i out of TMEM (for the
+//                last block of an item: the first scores of the next item, whose K / V sit in the other buffer), ahead
+//                of dQ_i = dS K, which waits for dS_i in shared memory.
+//   MMA warp B:  dV += P^T dO and dK += dS^T Q (issuing the 24 narrow MMAs of a block from one thread took a
+//                microsecond).  The completion of both warps' products frees P / dS and the Q / dO ring slot and
+//                publishes dQ_i.
+//   compute:     read S_i / dP_i, build P_i / dS_i in registers while the previous block's products still read the
+//                P / dS images, then store them.  The warps of chunks 2 and 3 own a staging block each: alternately
+//                they move dQ_{i-1} from TMEM through it (in the 128-byte swizzle, no bank conflicts) into the fp32
+//                accumulator with a TMA reduce-add, under the same proxy fence as P / dS, and at the end of an item
+//                they write dK and dV.
+//   TMA warp:    K / V (double-buffered for a padded head dim of 32) and the key bias of the next item, Q / dO blocks
+//                through a ring of two.
+// TMEM columns: S [0,128) dP [128,256) dV [256,..) dK [320,..) dQ [384,..) and [448,..) alternately.
+// Trace codes (thread 256 of CTA 0, row 0): 1 block start, 2 scores there, 3 P / dS in registers, 31 previous products
+// done, 32 P / dS stored, 33 dQ staged, 4 published, 5 last products done, 6 last dQ out, 7 dK / dV out; row 1 (MMA
+// warp A): 10 item, 11 first scores issued, 12 block, 13 next scores issued, 14 P / dS ready, 15 dQ issued.
+// Bounded wait whose polling loop is kept out of line: the persistent backward waits in many places.
+__device__ __noinline__ bool mbar_wait_slow(uint64_t* bar, uint32_t parity, volatile int* abort_flag, int* status, int detail) {
+  return mbar_wait(bar, parity, abort_flag, status, kErrAttnBarrierTimeout, detail);
+}
+__device__ __forceinline__ bool mbar_wait_ol(uint64_t* bar, uint32_t parity, volatile int* abort_flag, int* status, int detail) {
+  if (mbar_try_wait(bar, parity)) return true;
+  return mbar_wait_slow(bar, parity, abort_flag, status, detail);
+}
+constexpr int kBwsThreads = 608;   // 16 compute warps, two MMA-issuing warps, one TMA warp
+struct BwsBars {
+  uint64_t kv_full[2], kv_empty[2];   // by K / V buffer
+  uint64_t qdo_full[2], qdo_empty[2];
+  uint64_t s_full, s_free, p_ready, pds_free, dkv_free;
+  int item[2];               // work item by parity of its sequence number; -1: none left
+  int bias_nz[2];            // the key bias of that item has a non-zero entry
+};
+template <int DP>
+constexpr int bwd_ws_kv_bufs() { return DP == 32 ? 2 : 1; }
+template <int DP>
+constexpr int bwd_ws_smem() {
+  return (4 + 2 * bwd_ws_kv_bufs<DP>()) * kBlk * 128 + 4 * kBlk * 128 + 2 * kBlk * DP * 4 + 2 * kBlk * 4 + 256 + 1024;
+}
+static_assert(bwd_ws_smem<32>() <= 232448 && bwd_ws_smem<64>() <= 232448, "shared memory of the persistent backward");
+
+template <typename T, int DP>
+__global__ void __launch_bounds__(kBwsThreads, 1)
+attn_bwd_ws_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+                   const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_do,
+                   const __grid_constant__ CUtensorMap map_dq, AttnParams p) {
+  static_assert(DP == 32 || DP == 64, "one 64-column image per operand");
+  constexpr int kImg = kBlk * 128;                 // 16 KB: a [128 x 64] 16-bit image
+  constexpr int kPImg = 2 * kBlk * 128;            // 32 KB: a [128 x 128] 16-bit image
+  constexpr uint32_t kColDV = 256, kColDK = 320, kColDQ = 384;
+  // K / V are double-buffered where shared memory allows: the next item's K / V and first scores are then under way
+  // before this item's last products have been issued
+  constexpr int KVB = bwd_ws_kv_bufs<DP>();
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* k_img = smem;                           // [KVB]
+  uint8_t* v_img = k_img + KVB * kImg;             // [KVB]
+  uint8_t* q_img0 = v_img + KVB * kImg;            // [2]
+  uint8_t* do_img0 = q_img0 + 2 * kImg;            // [2]
+  uint8_t* p_img = do_img0 + 2 * kImg;
+  uint8_t* ds_img = p_img + kPImg;
+  float* dq_stage = reinterpret_cast<float*>(ds_img + kPImg);        // [8 compute warps][32][DP]
+  float* s_bias = dq_stage + 2 * kBlk * DP;                          // [2][128], log2 domain
+  BwsBars* bars = reinterpret_cast<BwsBars*>(s_bias + 2 * kBlk);
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 1);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  if (tid == 0) {
+    for (int i = 0; i < 2; ++i) { mbar_init(&bars->kv_full[i], 1); mbar_init(&bars->kv_empty[i], 1); }
+    for (int i = 0; i < 2; ++i) { mbar_init(&bars->qdo_full[i], 1); mbar_init(&bars->qdo_empty[i], 2); }
+    mbar_init(&bars->s_full, 1); mbar_init(&bars->s_free, 16); mbar_init(&bars->p_ready, 16);
+    mbar_init(&bars->pds_free, 2); mbar_init(&bars->dkv_free, 8);
+    *abort_flag = 0;
+    fence_barrier_init();
+  }
+  if (warp == 16) {
+    __syncwarp();
+    tmem_alloc(tmem_slot, 512);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = *tmem_slot;
+
+  const int n_q = (p.T + kBlk - 1) / kBlk;
+  const int total = n_q * p.H * p.B;
+  // item t: key block t % n_q (for a causal mask the block with the most query blocks first), head, batch
+  auto n_it_of = [&](int kb) { return p.causal ? n_q - kb : n_q; };
+
+  if (warp == 18) {
+    // =========================================================================== TMA producer (+ key bias)
+    int g = 0;
+    for (int n = 0;; ++n) {
+      int t = 0;
+      bool ok = true;
+      if (lane == 0) {
+        t = atomicAdd(p.work_counter, 1);
+        if (t >= total) t = -1;
+      }
+      t = __shfl_sync(0xffffffffu, t, 0);
+      const int kb = t < 0 ? 0 : t % n_q, bh = t < 0 ? 0 : t / n_q, h = bh % p.H, b = bh / p.H;
+      const int n_it = n_it_of(kb), i0 = n_q - n_it;
+      // the bias values are requested before the wait below
+      float bvals[4] = {0.f, 0.f, 0.f, 0.f};
+      if (p.key_bias != nullptr && t >= 0) {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const int key = kb * kBlk + lane * 4 + i;
+          if (key < p.T) bvals[i] = p.key_bias[static_cast<int64_t>(b) * p.T + key] * kLog2e;
+        }
+      }
+      // the K / V buffer, the bias slot and the item slot that this item takes are no longer read
+      if (lane == 0 && n >= KVB) ok = mbar_wait_ol(&bars->kv_empty[n % KVB], (n / KVB - 1) & 1, abort_flag, p.status, n);
+      ok = __shfl_sync(0xffffffffu, ok, 0);
+      if (!ok) break;
+      if (t < 0) {
+        if (lane == 0) { bars->item[n & 1] = -1; mbar_arrive(&bars->kv_full[n % KVB]); }
+        break;
+      }
+      if (p.key_bias != nullptr) {
+        float* dst = s_bias + (n & 1) * kBlk;
+        bool nz = false;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const float bv = bvals[i];
+          dst[lane * 4 + i] = bv;
+          nz = nz || bv != 0.f;
+        }
+        // an all-zero bias (no padding among these keys) lets the compute warps skip it
+        const bool any_nz = __any_sync(0xffffffffu, nz);
+        if (lane == 0) bars->bias_nz[n & 1] = any_nz ? 1 : 0;
+        __threadfence_block();
+      }
+      __syncwarp();
+      if (lane == 0) {
+        bars->item[n & 1] = t;
+        mbar_expect_tx(&bars->kv_full[n % KVB], 2 * kImg);
+        tma_load_4d(k_img + (n % KVB) * kImg, &map_k, &bars->kv_full[n % KVB], 0, kb * kBlk, h, b);
+        tma_load_4d(v_img + (n % KVB) * kImg, &map_v, &bars->kv_full[n % KVB], 0, kb * kBlk, h, b);
+        for (int it = 0; it < n_it; ++it) {
+          const int gi = g + it, slot = gi & 1;
+          if (gi >= 2) ok = mbar_wait_ol(&bars->qdo_empty[slot], ((gi >> 1) - 1) & 1, abort_flag, p.status, gi);
+          if (!ok) break;
+          mbar_expect_tx(&bars->qdo_full[slot], 2 * kImg);
+          tma_load_4d(q_img0 + slot * kImg, &map_q, &bars->qdo_full[slot], 0, (i0 + it) * kBlk, h, b);
+          tma_load_4d(do_img0 + slot * kImg, &map_do, &bars->qdo_full[slot], 0, (i0 + it) * kBlk, h, b);
+        }
+      }
+      ok = __shfl_sync(0xffffffffu, ok, 0);
+      if (!ok) break;
+      g += n_it;
+      if (p.trace != nullptr && lane == 0) {
+        // per-CTA totals in the third trace row: (items, blocks), (first item taken, last item taken)
+        long long* e = p.trace + (static_cast<size_t>(2) * 4096 + 2 * blockIdx.x) * 2;
+        const long long now = static_cast<long long>(globaltimer_ns());
+        if (n == 0) e[2] = now;
+        e[0] = n + 1; e[1] = g; e[3] = now;
+      }
+    }
+  } else if (warp == 16) {
+    // =========================================================================== MMA issuer A: S, dP and dQ
+    if (lane == 0) {
+      const uint32_t idesc_s = make_idesc_f16(kBlk, kBlk, false, false, p.is_bf16);     // Q K^T, dO V^T
+      const uint32_t idesc_dq = make_idesc_f16(kBlk, DP, false, true, p.is_bf16);       // dS K
+      const uint32_t dsa = smem_u32(ds_img);
+      auto issue_scores = [&](int gi, int kvb) -> bool {
+        const int slot = gi & 1;
+        const uint32_t ka = smem_u32(k_img + kvb * kImg), va = smem_u32(v_img + kvb * kImg);
+        if (gi > 0 && !mbar_wait_ol(&bars->s_free, (gi - 1) & 1, abort_flag, p.status, gi)) return false;
+        if (!mbar_wait_ol(&bars->qdo_full[slot], (gi >> 1) & 1, abort_flag, p.status, gi)) return false;
+        tc_fence_after();
+        const uint32_t qa = smem_u32(q_img0 + slot * kImg), da = smem_u32(do_img0 + slot * kImg);
+#pragma unroll
+        for (int k16 = 0; k16 < DP / 16; ++k16) tc_mma_f16(tmem, kmajor_desc(qa, k16), kmajor_desc(ka, k16), idesc_s, k16 > 0);
+#pragma unroll
+        for (int k16 = 0; k16 < DP / 16; ++k16) tc_mma_f16(tmem + 128, kmajor_desc(da, k16), kmajor_desc(va, k16), idesc_s, k16 > 0);
+        tc_commit(&bars->s_full);
+        return true;
+      };
+      int g = 0, mtr = 0;
+      bool ok = true, have_first = false;            // the scores of block g have been issued already
+      for (int n = 0; ok; ++n) {
+        if (!mbar_wait_ol(&bars->kv_full[n % KVB], (n / KVB) & 1, abort_flag, p.status, n)) break;
+        const int t = bars->item[n & 1];
+        if (t < 0) break;
+        const int n_it = n_it_of(t % n_q);
+        const int kvb = n % KVB;
+        const uint32_t ka = smem_u32(k_img + kvb * kImg);
+        attn_trace(p.trace, 1, mtr, 10);
+        if (!have_first) ok = issue_scores(g, kvb);
+        have_first = false;
+        attn_trace(p.trace, 1, mtr, 11);
+        for (int it = 0; it < n_it && ok; ++it) {
+          const int gi = g + it, slot = gi & 1;
+          attn_trace(p.trace, 1, mtr, 12);
+          if (it + 1 < n_it) {
+            ok = issue_scores(gi + 1, kvb);
+            if (!ok) break;
+          } else if (KVB == 2) {
+            // the first scores of the next item, whose K / V sit in the other buffer
+            if (!mbar_wait_ol(&bars->kv_full[(n + 1) % KVB], ((n + 1) / KVB) & 1, abort_flag, p.status, n)) { ok = false; break; }
+            if (bars->item[(n + 1) & 1] >= 0) {
+              ok = issue_scores(gi + 1, (n + 1) % KVB);
+              if (!ok) break;
+              have_first = true;
+            }
+          }
+          attn_trace(p.trace, 1, mtr, 13);
+          ok = mbar_wait_ol(&bars->p_ready, gi & 1, abort_flag, p.status, gi);
+          if (!ok) break;
+          tc_fence_after();
+          attn_trace(p.trace, 1, mtr, 14);
+#pragma unroll
+          for (int k16 = 0; k16 < kBlk / 16; ++k16)   // dQ[q, d] = sum_key dS[q, key] K[key, d]
+            tc_mma_f16(tmem + kColDQ + slot * 64, kmajor_desc(dsa, k16), mnmajor_desc(ka, k16), idesc_dq, k16 > 0);
+          tc_commit(&bars->pds_free);
+          tc_commit(&bars->qdo_empty[slot]);           // covers S / dP of this block as well
+          if (it == n_it - 1) tc_commit(&bars->kv_empty[kvb]);
+          attn_trace(p.trace, 1, mtr, 15);
+        }
+        g += n_it;
+      }
+    }
+  } else if (warp == 17) {
+    // =========================================================================== MMA issuer B: dV and dK
+    if (lane == 0) {
+      const uint32_t idesc_tt = make_idesc_f16(kBlk, DP, true, true, p.is_bf16);        // P^T dO, dS^T Q
+      const uint32_t pa = smem_u32(p_img), dsa = smem_u32(ds_img);
+      int g = 0;
+      bool ok = true;
+      for (int n = 0; ok; ++n) {
+        if (!mbar_wait_ol(&bars->kv_full[n % KVB], (n / KVB) & 1, abort_flag, p.status, n)) break;
+        const int t = bars->item[n & 1];
+        if (t < 0) break;
+        const int n_it = n_it_of(t % n_q);
+        for (int it = 0; it < n_it && ok; ++it) {
+          const int gi = g + it, slot = gi & 1;
+          ok = mbar_wait_ol(&bars->qdo_full[slot], (gi >> 1) & 1, abort_flag, p.status, gi) &&
+               mbar_wait_ol(&bars->p_ready, gi & 1, abort_flag, p.status, gi);
+          // the compute warps have read the previous item's dK / dV out of TMEM
+          if (ok && it == 0 && n > 0) ok = mbar_wait_ol(&bars->dkv_free, (n - 1) & 1, abort_flag, p.status, n);
+          if (!ok) break;
+          tc_fence_after();
+          const uint32_t qa = smem_u32(q_img0 + slot * kImg), da = smem_u32(do_img0 + slot * kImg);
+          const uint32_t acc = it > 0 ? 1u : 0u;
+#pragma unroll
+          for (int k16 = 0; k16 < kBlk / 16; ++k16)   // dV[key, d] += sum_q P[q, key] dO[q, d]
+            tc_mma_f16(tmem + kColDV, mnmajor_desc(pa, k16), mnmajor_desc(da, k16), idesc_tt, (k16 > 0) ? 1u : acc);
+#pragma unroll
+          for (int k16 = 0; k16 < kBlk / 16; ++k16)   // dK[key, d] += sum_q dS[q, key] Q[q, d]
+            tc_mma_f16(tmem + kColDK, mnmajor_desc(dsa, k16), mnmajor_desc(qa, k16), idesc_tt, (k16 > 0) ? 1u : acc);
+          tc_commit(&bars->pds_free);
+          tc_commit(&bars->qdo_empty[slot]);
+        }
+        g += n_it;
+      }
+    }
+  } else {
+    // =========================================================================== compute warps
+    // Four threads per query row, one per 32-key chunk of the block (sixteen warps: four per scheduler, so that the
+    // TMEM and exponential latencies of one warp are covered by the others).  The warps of chunks 2 and 3 also own a
+    // staging block each: they write out dQ (alternately, block by block) and, at the end of an item, dK and dV.
+    const int r = tid & 127;                         // query row inside a block == TMEM lane
+    const int qt = tid >> 7;                         // this thread's 32-key chunk of the block
+    const int wq = warp & 3;                         // this warp's 32-row block
+    const bool owner = qt >= 2;
+    const uint32_t lane_base = static_cast<uint32_t>(wq * 32) << 16;
+    const float sc2 = p.scale * kLog2e;
+    const int64_t ld = static_cast<int64_t>(p.H) * 3 * p.dh;
+    float* stg = dq_stage + (((qt & 1) * 4 + wq) * 32) * DP;   // an owner warp's [32][DP] fp32 staging rows
+    int g = 0, ntr = 0;
+    bool ok = true;
+    long long* tr = tid == 256 ? p.trace : nullptr;   // an owner thread
+
+    // dQ of global block gi (TMEM column set gi & 1) -> this warp's staging rows: boxes of 32 rows x 128 bytes in the
+    // 128-byte swizzle of the tensor map (16-byte chunk j of row l sits at chunk j ^ (l & 7): no bank conflicts)
+    auto dq_ld = [&](int gi, int c, uint32_t (&raw)[32]) {
+      tmem_ld_32x32(tmem + kColDQ + (gi & 1) * 64 + lane_base + c * 32, raw);
+    };
+    auto dq_st = [&](int c, uint32_t (&raw)[32]) {
+      tmem_wait_ld_for(raw);
+      uint8_t* row = reinterpret_cast<uint8_t*>(stg) + c * 4096 + lane * 128;
+#pragma unroll
+      for (int j = 0; j < 8; ++j)
+        *reinterpret_cast<uint4*>(row + ((j ^ (lane & 7)) << 4)) = make_uint4(raw[4 * j], raw[4 * j + 1], raw[4 * j + 2], raw[4 * j + 3]);
+    };
+    // staging rows -> fp32 accumulator by TMA reduce-add (lane 0, after the warp's proxy fences and __syncwarp)
+    auto dq_reduce = [&](int h, int b, int q_first) {
+      const int row0 = q_first + wq * 32;
+      if (row0 < p.T) {
+        // rows past the sequence end carry exact zeros (their dS is zero), so a box that overlaps them adds nothing
+        const int grow = (b * p.H + h) * p.T + row0;
+#pragma unroll
+        for (int c = 0; c < DP / 32; ++c) tma_reduce_add_2d(&map_dq, reinterpret_cast<uint8_t*>(stg) + c * 4096, c * 32, grow);
+      }
+      bulk_commit_group();
+    };
+
+    for (int n = 0; ok; ++n) {
+      if (!mbar_wait_ol(&bars->kv_full[n % KVB], (n / KVB) & 1, abort_flag, p.status, n)) { ok = false; break; }
+      const int t = bars->item[n & 1];
+      if (t < 0) break;
+      const int kb = t % n_q, bh = t / n_q, h = bh % p.H, b = bh / p.H;
+      const int k0 = kb * kBlk;
+      const int n_it = n_it_of(kb), i0 = n_q - n_it;
+      const bool has_bias = p.key_bias != nullptr && bars->bias_nz[n & 1] != 0;
+      const float* sbias = s_bias + (n & 1) * kBlk + qt * 32;
+      const int64_t stat0 = (static_cast<int64_t>(b) * p.H + h) * p.T;
+      // row statistics of the first block; those of block it + 1 are requested while block it is processed
+      float lse_nx = 0.f, dl_nx = 0.f;
+      if (i0 * kBlk + r < p.T) { lse_nx = p.lse[stat0 + i0 * kBlk + r]; dl_nx = p.delta[stat0 + i0 * kBlk + r]; }
+      for (int it = 0; it < n_it; ++it) {
+        const int gi = g + it, i = i0 + it, q0 = i * kBlk;
+        const int q_idx = q0 + r;
+        const float lse2 = lse_nx;
+        const float nds = -dl_nx * p.scale;
+        lse_nx = 0.f; dl_nx = 0.f;
+        if (it + 1 < n_it && q_idx + kBlk < p.T) { lse_nx = p.lse[stat0 + q_idx + kBlk]; dl_nx = p.delta[stat0 + q_idx + kBlk]; }
+        // the owner warps of chunk 2 + ((gi - 1) & 1) write out the previous block's dQ
+        const bool my_dq = it > 0 && owner && ((gi - 1) & 1) == (qt & 1);
+        attn_trace(tr, 0, ntr, 1);
+        if (!mbar_wait_ol(&bars->s_full, gi & 1, abort_flag, p.status, gi)) { ok = false; break; }
+        tc_fence_after();
+        attn_trace(tr, 0, ntr, 2);
+        const bool tail = (k0 + kBlk > p.T) || (q0 + kBlk > p.T);
+        const bool cdiag = p.causal && i == kb;
+        // P / dS of this thread's chunk are computed into registers while the products of the previous block still
+        // read the P / dS images; they are stored once those products are done.
+        // Diagonal block of a causal mask: key chunks left of this warp's rows are plain, the chunk on the diagonal is
+        // tested key by key, chunks to the right are zero.  Blocks that reach past the sequence end are tested everywhere.
+        uint32_t pk[16], dk[16];
+        if (!tail && cdiag && qt > wq) {
+#pragma unroll
+          for (int j = 0; j < 16; ++j) { pk[j] = 0u; dk[j] = 0u; }
+        } else {
+          const bool masked = tail || (cdiag && qt == wq);
+#pragma unroll
+          for (int hf = 0; hf < 2; ++hf) {
+            uint32_t rs[16], rp[16];
+            tmem_ld_32x16(tmem + lane_base + qt * 32 + hf * 16, rs);
+            tmem_ld_32x16(tmem + 128 + lane_base + qt * 32 + hf * 16, rp);
+            tmem_wait_ld_for(rs);
+            tmem_wait_ld_for(rp);
+            if (!masked) {
+              if (has_bias) bwd_half_regs<false, true, T>(rs, rp, sbias + hf * 16, sc2, lse2, p.scale, nds, 0, 0, 0, false, pk + hf * 8, dk + hf * 8);
+              else bwd_half_regs<false, false, T>(rs, rp, nullptr, sc2, lse2, p.scale, nds, 0, 0, 0, false, pk + hf * 8, dk + hf * 8);
+            } else {
+              if (has_bias) bwd_half_regs<true, true, T>(rs, rp, sbias + hf * 16, sc2, lse2, p.scale, nds, k0 + qt * 32 + hf * 16, q_idx, p.T, cdiag, pk + hf * 8, dk + hf * 8);
+              else bwd_half_regs<true, false, T>(rs, rp, nullptr, sc2, lse2, p.scale, nds, k0 + qt * 32 + hf * 16, q_idx, p.T, cdiag, pk + hf * 8, dk + hf * 8);
+            }
+          }
+        }
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&bars->s_free);     // last read of S / dP: the next block's scores may overwrite them
+        attn_trace(tr, 0, ntr, 3);
+        // the products of the previous block have finished reading P / dS, and its dQ is complete
+        if (gi > 0 && !mbar_wait_ol(&bars->pds_free, (gi - 1) & 1, abort_flag, p.status, gi)) ok = false;
+        tc_fence_after();
+        attn_trace(tr, 0, ntr, 31);
+        const bool drain = my_dq && ok;
+        store_packed_chunk(p_img, r, qt * 32, pk);
+        store_packed_chunk(ds_img, r, qt * 32, dk);
+        attn_trace(tr, 0, ntr, 32);
+        if (drain) {
+          uint32_t dq_raw[32];
+          if (lane == 0) bulk_wait_group_read0();      // the previous reduction has read the staging rows
+          __syncwarp();
+          dq_ld(gi - 1, 0, dq_raw);
+          dq_st(0, dq_raw);
+          if constexpr (DP == 64) {
+            dq_ld(gi - 1, 1, dq_raw);
+            dq_st(1, dq_raw);
+          }
+          tc_fence_before();
+        }
+        attn_trace(tr, 0, ntr, 33);
+        fence_proxy_async();                         // P / dS (and the staged dQ) become visible to the async proxy
+        __syncwarp();
+        if (lane == 0) {
+          mbar_arrive(&bars->p_ready);
+          if (drain) dq_reduce(h, b, q0 - kBlk);
+        }
+        if (!ok) break;
+        attn_trace(tr, 0, ntr, 4);
+      }
+      if (!ok) break;
+      g += n_it;
+      if (!owner) continue;
+      // ---- owner warps: the item's last dQ, then its dK (chunk 2's warps) / dV (chunk 3's warps)
+      const int g_last = g - 1;
+      if (!mbar_wait_ol(&bars->pds_free, g_last & 1, abort_flag, p.status, g_last)) { ok = false; break; }
+      tc_fence_after();
+      attn_trace(tr, 0, ntr, 5);
+      if ((g_last & 1) == (qt & 1)) {
+        uint32_t dq_raw[32];
+        if (lane == 0) bulk_wait_group_read0();
+        __syncwarp();
+#pragma unroll
+        for (int c = 0; c < DP / 32; ++c) {
+          dq_ld(g_last, c, dq_raw);
+          dq_st(c, dq_raw);
+        }
+        tc_fence_before();
+        fence_proxy_async();
+        __syncwarp();
+        if (lane == 0) dq_reduce(h, b, (i0 + n_it - 1) * kBlk);
+      }
+      attn_trace(tr, 0, ntr, 6);
+      {
+        // rows go through the warp's staging block so that each global store instruction writes one row's contiguous
+        // bytes instead of one column of 32 rows that lie kilobytes apart
+        uint32_t raw[32];
+        const uint32_t col = qt == 2 ? kColDK : kColDV;
+        tmem_ld_32x32(tmem + col + lane_base, raw);
+        if (lane == 0) bulk_wait_group_read0();      // the reduction that reads the staging block has done so
+        __syncwarp();
+        T* stage = reinterpret_cast<T*>(stg);        // [32][DP]
+#pragma unroll
+        for (int c = 0; c < DP / 32; ++c) {
+          if (c > 0) tmem_ld_32x32(tmem + col + lane_base + c * 32, raw);
+          tmem_wait_ld_for(raw);
+          uint4* d4 = reinterpret_cast<uint4*>(stage + lane * DP + c * 32);
+#pragma unroll
+          for (int q = 0; q < 4; ++q) {
+            uint4 u;
+            u.x = pack_pair<T>(__uint_as_float(raw[q * 8 + 0]), __uint_as_float(raw[q * 8 + 1]));
+            u.y = pack_pair<T>(__uint_as_float(raw[q * 8 + 2]), __uint_as_float(raw[q * 8 + 3]));
+            u.z = pack_pair<T>(__uint_as_float(raw[q * 8 + 4]), __uint_as_float(raw[q * 8 + 5]));
+            u.w = pack_pair<T>(__uint_as_float(raw[q * 8 + 6]), __uint_as_float(raw[q * 8 + 7]));
+            d4[q] = u;
+          }
+        }
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&bars->dkv_free);   // the next item's products may overwrite the accumulators
+        const int row0 = k0 + wq * 32;
+        const int rows = min(32, p.T - row0);
+        T* dst = reinterpret_cast<T*>(p.dqkv) + (static_cast<int64_t>(b) * p.T + row0) * ld + h * 3 * p.dh + (qt == 2 ? p.dh : 2 * p.dh);
+        for (int d = lane; d < p.dh; d += 32) {
+          for (int r0 = 0; r0 < rows; r0 += 8) {
+            T v[8];
+#pragma unroll
+            for (int u = 0; u < 8; ++u) v[u] = stage[min(r0 + u, 31) * DP + d];
+#pragma unroll
+            for (int u = 0; u < 8; ++u)
+              if (r0 + u < rows) dst[(r0 + u) * ld + d] = v[u];
+          }
+        }
+        __syncwarp();                                // the rows have been read before the block is staged into again
+      }
+      attn_trace(tr, 0, ntr, 7);
+    }
+    if (lane == 0) bulk_wait_group0();
+    if (!ok) *abort_flag = 1;
+  }
+
+  if (*abort_flag) {
+    for (int i = 0; i < 32; ++i) __nanosleep(1000);
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 16) {
+    tc_fence_after();
+    tmem_dealloc(tmem, 512);
   }
 }
 
@@ -1241,6 +1761,7 @@ constexpr int bwd_smem() {
 
 struct AttnMaps {
   CUtensorMap q, k, v, d_out;
+  CUtensorMap dq;   // fp32 dQ accumulator [B*H*T, DP] (persistent backward)
 };
 
 template <typename T, int DP>
@@ -1275,14 +1796,26 @@ static void launch_fwd(const AttnMaps& m, const AttnParams& p, cudaStream_t s) {
 }
 template <typename T, int DP>
 static void launch_bwd(const AttnMaps& m, const AttnParams& p, cudaStream_t s) {
-  auto kern = attn_bwd_kernel<T, DP>;
-  static bool done = false;
-  if (!done) {
-    C10_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, bwd_smem<DP>()));
-    done = true;
+  if constexpr (DP <= 64) {
+    auto kern = attn_bwd_ws_kernel<T, DP>;
+    static bool done = false;
+    if (!done) {
+      C10_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, bwd_ws_smem<DP>()));
+      done = true;
+    }
+    const int items = ((p.T + kBlk - 1) / kBlk) * p.H * p.B;
+    const int sms = at::cuda::getCurrentDeviceProperties()->multiProcessorCount;
+    kern<<<std::min(items, sms), kBwsThreads, bwd_ws_smem<DP>(), s>>>(m.q, m.k, m.v, m.d_out, m.dq, p);
+  } else {
+    auto kern = attn_bwd_kernel<T, DP>;
+    static bool done = false;
+    if (!done) {
+      C10_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, bwd_smem<DP>()));
+      done = true;
+    }
+    dim3 grid((p.T + kBlk - 1) / kBlk, p.H, p.B);
+    kern<<<grid, kBwdThreads, bwd_smem<DP>(), s>>>(m.q, m.k, m.v, m.d_out, p);
   }
-  dim3 grid((p.T + kBlk - 1) / kBlk, p.H, p.B);
-  kern<<<grid, kBwdThreads, bwd_smem<DP>(), s>>>(m.q, m.k, m.v, m.d_out, p);
   C10_CUDA_KERNEL_LAUNCH_CHECK();
 }
 
@@ -1396,13 +1929,16 @@ torch::Tensor attention_bwd(torch::Tensor dout, torch::Tensor qkv, torch::Tensor
     TORCH_CHECK(trace->scalar_type() == torch::kInt64 && trace->numel() >= 2 * 4096 * 2 && trace->is_cuda());
     p.trace = reinterpret_cast<long long*>(trace->data_ptr<int64_t>());
   }
+  TORCH_CHECK(p.trace == nullptr || trace->numel() >= 3 * 4096 * 2, "the backward trace has three rows");
   TORCH_CHECK(dout.is_contiguous() && dout.numel() == out.numel() && dout.scalar_type() == qkv.scalar_type());
   auto dqkv = torch::empty_like(qkv);
   if (qkv.numel() == 0) return dqkv;
   auto f32 = qkv.options().dtype(torch::kFloat32);
   auto delta = torch::empty({p.B, p.H, p.T}, f32);
   const int DPh = padded_dim(p.dh);
-  auto dq_acc = torch::zeros({p.B, p.H, p.T, DPh}, f32);
+  // fp32 dQ accumulator [B, H, T, DPh], followed by the work counter of the persistent kernel (zeroed with it)
+  const int64_t dq_elems = static_cast<int64_t>(p.B) * p.H * p.T * DPh;
+  auto dq_acc = torch::zeros({dq_elems + 32}, f32);
   auto stream = at::cuda::getCurrentCUDAStream();
   const int64_t rows = static_cast<int64_t>(p.B) * p.T * p.H;
   if (p.is_bf16) {
@@ -1431,9 +1967,12 @@ torch::Tensor attention_bwd(torch::Tensor dout, torch::Tensor qkv, torch::Tensor
       m.d_out = make_tma_4d(dout.data_ptr(), dh, T, H, B, H * dh * 2, dh * 2, T * H * dh * 2);
     }
   }
+  if (DPh <= 64)
+    m.dq = make_tma_2d_store(dq_acc.data_ptr<float>(), static_cast<uint64_t>(p.B) * p.H * p.T, DPh, DPh, 4, false);
   p.lse = lse.data_ptr<float>();
   p.delta = delta.data_ptr<float>();
   p.dq_acc = dq_acc.data_ptr<float>();
+  p.work_counter = reinterpret_cast<int*>(dq_acc.data_ptr<float>() + dq_elems);
   p.dqkv = dqkv.data_ptr();
   DISPATCH_ATTN(launch_bwd, m, p, stream)
   if (p.is_bf16) {
