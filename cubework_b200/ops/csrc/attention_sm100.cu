@@ -387,6 +387,15 @@ __device__ __forceinline__ float chunk_exp(const uint32_t (&raw)[32], const floa
   return (ll[0] + ll[1]) + (ll[2] + ll[3]);
 }
 
+// Bounded wait whose polling loop is kept out of line: the persistent kernels wait in many places, and their
+// instruction footprint decides how often the warps of the different roles miss the instruction cache.
+__device__ __noinline__ bool mbar_wait_slow(uint64_t* bar, uint32_t parity, volatile int* abort_flag, int* status, int detail) {
+  return mbar_wait(bar, parity, abort_flag, status, kErrAttnBarrierTimeout, detail);
+}
+__device__ __forceinline__ bool mbar_wait_ol(uint64_t* bar, uint32_t parity, volatile int* abort_flag, int* status, int detail) {
+  if (mbar_try_wait(bar, parity)) return true;
+  return mbar_wait_slow(bar, parity, abort_flag, status, detail);
+}
 constexpr int kWsThreads = 384;
 constexpr int kWsKRing = 2, kWsBiasRing = 4;
 template <int DP>
@@ -466,7 +475,7 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
       const int n_kv = n_kv_of(qb);
       bool ok = true;
       if (lane == 0) {
-        ok = mbar_wait(&bars->q_empty, (tile_it & 1) ^ 1, abort_flag, p.status, kErrAttnBarrierTimeout, t);
+        ok = mbar_wait_ol(&bars->q_empty, (tile_it & 1) ^ 1, abort_flag, p.status, t);
         if (ok) {
           mbar_expect_tx(&bars->q_full, kImg);
           tma_load_4d(q_img, &map_q, &bars->q_full, 0, qb * kBlk, h, b);
@@ -475,7 +484,7 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
       for (int j = 0; j < n_kv; ++j) {
         const int ks = kcount % kWsKRing;
         if (lane == 0)
-          ok = ok && mbar_wait(&bars->k_empty[ks], ((kcount / kWsKRing) & 1) ^ 1, abort_flag, p.status, kErrAttnBarrierTimeout, t);
+          ok = ok && mbar_wait_ol(&bars->k_empty[ks], ((kcount / kWsKRing) & 1) ^ 1, abort_flag, p.status, t);
         ok = __shfl_sync(0xffffffffu, ok, 0);
         if (!ok) break;
         if (p.key_bias != nullptr) {
@@ -495,7 +504,7 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
         if (lane == 0) {
           mbar_expect_tx(&bars->k_full[ks], kImg);
           tma_load_4d(k_img + ks * kImg, &map_k, &bars->k_full[ks], 0, j * kBlk, h, b);
-          ok = mbar_wait(&bars->v_empty, (vcount & 1) ^ 1, abort_flag, p.status, kErrAttnBarrierTimeout, t);
+          ok = mbar_wait_ol(&bars->v_empty, (vcount & 1) ^ 1, abort_flag, p.status, t);
           if (ok) {
             mbar_expect_tx(&bars->v_full, kImg);
             tma_load_4d(v_img, &map_v, &bars->v_full, 0, j * kBlk, h, b);
@@ -515,7 +524,7 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
       bool ok = true;
       auto issue_s = [&](bool last) -> bool {
         const int ks = kcount % kWsKRing;
-        if (!mbar_wait(&bars->k_full[ks], (kcount / kWsKRing) & 1, abort_flag, p.status, kErrAttnBarrierTimeout, kcount)) return false;
+        if (!mbar_wait_ol(&bars->k_full[ks], (kcount / kWsKRing) & 1, abort_flag, p.status, kcount)) return false;
         tc_fence_after();
 #pragma unroll
         for (int k16 = 0; k16 < DP / 16; ++k16)
@@ -529,11 +538,11 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
       for (int t = first; t < tiles && ok && !*abort_flag; t += stride, ++tile_it) {
         const int qb = n_qb - 1 - t / bh_total;
         const int n_kv = n_kv_of(qb);
-        ok = mbar_wait(&bars->q_full, tile_it & 1, abort_flag, p.status, kErrAttnBarrierTimeout, t);
+        ok = mbar_wait_ol(&bars->q_full, tile_it & 1, abort_flag, p.status, t);
         ok = ok && issue_s(n_kv == 1);
         for (int j = 0; j < n_kv && ok; ++j) {
           // the group has read S_j for the last time: S_{j+1} goes first, it is what the group needs soonest
-          ok = mbar_wait(&bars->s_free, fcount & 1, abort_flag, p.status, kErrAttnBarrierTimeout, t);
+          ok = mbar_wait_ol(&bars->s_free, fcount & 1, abort_flag, p.status, t);
           if (!ok) break;
           ++fcount;
           if (j + 1 < n_kv) {
@@ -541,10 +550,10 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
             ok = issue_s(j + 1 == n_kv - 1);
             if (!ok) break;
           }
-          ok = mbar_wait(&bars->p_ready, pcount & 1, abort_flag, p.status, kErrAttnBarrierTimeout, t);
+          ok = mbar_wait_ol(&bars->p_ready, pcount & 1, abort_flag, p.status, t);
           if (!ok) break;
           ++pcount;
-          ok = mbar_wait(&bars->v_full, vcount & 1, abort_flag, p.status, kErrAttnBarrierTimeout, t);
+          ok = mbar_wait_ol(&bars->v_full, vcount & 1, abort_flag, p.status, t);
           if (!ok) break;
           tc_fence_after();
 #pragma unroll
@@ -576,7 +585,7 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
       for (int j = 0; j < n_kv; ++j) {
         const int k0 = j * kBlk;
         attn_trace(tr, 0, ntr, 1);
-        if (!mbar_wait(&bars->s_full, scount & 1, abort_flag, p.status, kErrAttnBarrierTimeout, t)) { ok = false; break; }
+        if (!mbar_wait_ol(&bars->s_full, scount & 1, abort_flag, p.status, t)) { ok = false; break; }
         ++scount;
         tc_fence_after();
         attn_trace(tr, 0, ntr, 2);
@@ -631,7 +640,7 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
         m_run = m_new;
         if (j > 0) {
           // the previous P V has landed in O: rescale it in place before more is added
-          if (!mbar_wait(&bars->o_full, ocount & 1, abort_flag, p.status, kErrAttnBarrierTimeout, t)) { ok = false; break; }
+          if (!mbar_wait_ol(&bars->o_full, ocount & 1, abort_flag, p.status, t)) { ok = false; break; }
           ++ocount;
           tc_fence_after();
           attn_trace(tr, 0, ntr, 4);
@@ -707,7 +716,7 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
       }
       if (!ok) break;
       // ---- the tile's output: the last P V has landed
-      if (!mbar_wait(&bars->o_full, ocount & 1, abort_flag, p.status, kErrAttnBarrierTimeout, t)) { ok = false; break; }
+      if (!mbar_wait_ol(&bars->o_full, ocount & 1, abort_flag, p.status, t)) { ok = false; break; }
       ++ocount;
       tc_fence_after();
       attn_trace(tr, 0, ntr, 8);
@@ -1293,14 +1302,6 @@ __device__ __forceinline__ void store_packed_chunk(uint8_t* img, int r, int c0, 
 // Trace codes (thread 256 of CTA 0, row 0): 1 block start, 2 scores there, 3 P / dS in registers, 31 previous products
 // done, 32 P / dS stored, 33 dQ staged, 4 published, 5 last products done, 6 last dQ out, 7 dK / dV out; row 1 (MMA
 // warp A): 10 item, 11 first scores issued, 12 block, 13 next scores issued, 14 P / dS ready, 15 dQ issued.
-// Bounded wait whose polling loop is kept out of line: the persistent backward waits in many places.
-__device__ __noinline__ bool mbar_wait_slow(uint64_t* bar, uint32_t parity, volatile int* abort_flag, int* status, int detail) {
-  return mbar_wait(bar, parity, abort_flag, status, kErrAttnBarrierTimeout, detail);
-}
-__device__ __forceinline__ bool mbar_wait_ol(uint64_t* bar, uint32_t parity, volatile int* abort_flag, int* status, int detail) {
-  if (mbar_try_wait(bar, parity)) return true;
-  return mbar_wait_slow(bar, parity, abort_flag, status, detail);
-}
 constexpr int kBwsThreads = 608;   // 16 compute warps, two MMA-issuing warps, one TMA warp
 struct BwsBars {
   uint64_t kv_full[2], kv_empty[2];   // by K / V buffer
