@@ -169,8 +169,10 @@ __device__ __forceinline__ TileInfo tile_info(const GgsParams& p, int owner, int
       tm += me * p.m_rps;
     } else {
       const int q = tm - p.m_rps;
-      const int pnl = q / (n - 1), si = q - pnl * (n - 1);
-      tm = ((me + n - 1 - si) % n) * p.m_rps + pnl;
+      const int pnl = fast_div(q, n - 1), si = q - pnl * (n - 1);
+      int src = me + n - 1 - si;                      // in [me, me + n - 1]
+      if (src >= n) src -= n;
+      tm = src * p.m_rps + pnl;
     }
   }
   TileInfo t;
@@ -527,8 +529,9 @@ gather_gemm_scatter_kernel(const __grid_constant__ CUtensorMap tma_a, const __gr
       const int v = bid + sc.ip * G;
       ++sc.ip;
       push_tile = true;
-      li = v / (p.sn - 1);
-      owner = (p.sme + 1 + v % (p.sn - 1)) % p.sn;
+      li = fast_div(v, p.sn - 1);
+      owner = p.sme + 1 + (v - li * (p.sn - 1));    // in [sme + 1, sme + sn - 1]
+      if (owner >= p.sn) owner -= p.sn;
       return true;
     }
     if (sc.io >= no) return false;

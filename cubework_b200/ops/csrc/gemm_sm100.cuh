@@ -72,21 +72,31 @@ struct OutType { using type = InT; };
 template <typename InT>
 struct OutType<InT, true> { using type = float; };
 
+// x / d for 0 <= x < 2^22 and d >= 1 through a float reciprocal and one correction step: a handful of instructions
+// where the integer division by a run-time divisor is a long dependent chain.  Every role of the persistent kernels
+// decodes its tiles with several such divisions, on the critical path between two tiles.
+__device__ __forceinline__ int fast_div(int x, int d) {
+  int q = __float2int_rz(__int2float_rn(x) * __frcp_rn(__int2float_rn(d)));
+  const int r = x - q * d;
+  q += (r >= d ? 1 : 0) - (r < 0 ? 1 : 0);
+  return q;
+}
+
 // Work item -> (tile_m, tile_n, k-block range).  Tiles are walked in groups of 16 row-blocks so the CTAs
 // that run concurrently share A and B panels in L2.
 __device__ __forceinline__ void decode_work(int w, int num_tiles, int tiles_m, int tiles_n, int kb_total, int splits,
                                             int& tile_m, int& tile_n, int& kb0, int& kb1) {
-  const int split = w / num_tiles;
+  const int split = splits > 1 ? fast_div(w, num_tiles) : 0;
   const int t = w - split * num_tiles;
   constexpr int kGroup = 16;
   const int per_group = kGroup * tiles_n;
-  const int group = t / per_group;
+  const int group = fast_div(t, per_group);
   const int first_m = group * kGroup;
   const int gsz = min(tiles_m - first_m, kGroup);
   const int in_group = t - group * per_group;
-  tile_m = first_m + in_group % gsz;
-  tile_n = in_group / gsz;
-  const int per = (kb_total + splits - 1) / splits;
+  tile_n = gsz == kGroup ? in_group >> 4 : fast_div(in_group, gsz);
+  tile_m = first_m + in_group - tile_n * gsz;
+  const int per = splits > 1 ? fast_div(kb_total + splits - 1, splits) : kb_total;
   kb0 = split * per;
   kb1 = min(kb0 + per, kb_total);
 }
