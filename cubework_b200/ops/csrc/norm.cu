@@ -279,24 +279,24 @@ ln_fwd_warp_kernel(const T* __restrict__ x, const T* __restrict__ res, const flo
   }
 }
 
-// Backward of the above.  Each lane keeps dgamma / dbeta of its columns in registers over all the rows of its warp;
-// the eight warps of a CTA combine them in shared memory and the CTA writes one partial row (summed by colsum2).
+// Backward of the above.  Each warp keeps the dgamma / dbeta partial sums of its rows in a shared-memory strip of its
+// own (in registers they cost 112 registers per thread at H = 1600 and held the kernel at eight warps per SM, where it
+// was bound by latency); the warps of a CTA are added up at the end and the CTA writes one partial row (summed by
+// colsum2).
 template <typename T, int NV, bool HAS_RES>
-__global__ void __launch_bounds__(32 * kWarpRows, 1)
+__global__ void __launch_bounds__(32 * kWarpRows, 2)
 ln_bwd_warp_kernel(const T* __restrict__ dy, const T* __restrict__ x, const float* __restrict__ mean,
                    const float* __restrict__ rstd, const float* __restrict__ gamma, const T* __restrict__ dres,
                    T* __restrict__ dx, float* __restrict__ part_dgamma, float* __restrict__ part_dbeta, int rows, int H) {
-  extern __shared__ float sacc[];            // [2][H]
+  extern __shared__ __align__(16) float sacc[];            // [kWarpRows][2][H]
   const int lane = threadIdx.x & 31;
   const int warp = blockIdx.x * kWarpRows + (threadIdx.x >> 5);
   const int nwarps = gridDim.x * kWarpRows;
   const float inv_h = 1.0f / H;
-  float dg[NV][8], db[NV][8];
-#pragma unroll
-  for (int v = 0; v < NV; ++v)
-#pragma unroll
-    for (int i = 0; i < 8; ++i) { dg[v][i] = 0.f; db[v][i] = 0.f; }
-  for (int i = threadIdx.x; i < 2 * H; i += blockDim.x) sacc[i] = 0.f;
+  float* wdg = sacc + static_cast<size_t>(threadIdx.x >> 5) * 2 * H;
+  float* wdb = wdg + H;
+  for (int i = lane * 4; i < 2 * H; i += 128) *reinterpret_cast<float4*>(wdg + i) = make_float4(0.f, 0.f, 0.f, 0.f);
+  __syncwarp();
 
   for (int row = warp; row < rows; row += nwarps) {
     const size_t base = static_cast<size_t>(row) * H;
@@ -308,7 +308,25 @@ ln_bwd_warp_kernel(const T* __restrict__ dy, const T* __restrict__ x, const floa
       xr[v] = ok ? *reinterpret_cast<const uint4*>(x + base + c) : make_uint4(0, 0, 0, 0);
       gr[v] = ok ? *reinterpret_cast<const uint4*>(dy + base + c) : make_uint4(0, 0, 0, 0);
     }
+    // requests that cost no registers: this row's residual gradient (read in the second pass) and the next row's
+    // operands go to L2 while the first pass runs
+    {
+      const size_t nbase = static_cast<size_t>(row + nwarps) * H;
+      const bool has_next = row + nwarps < rows;
+#pragma unroll
+      for (int v = 0; v < NV; ++v) {
+        const int c = (v * 32 + lane) * 8;
+        if (c < H) {
+          if (HAS_RES) asm volatile("prefetch.global.L2 [%0];" ::"l"(dres + base + c));
+          if (has_next) {
+            asm volatile("prefetch.global.L2 [%0];" ::"l"(x + nbase + c));
+            asm volatile("prefetch.global.L2 [%0];" ::"l"(dy + nbase + c));
+          }
+        }
+      }
+    }
     const float mu = mean[row], rs = rstd[row];
+    const float nmr = -mu * rs;
     float s1 = 0.f, s2 = 0.f;
 #pragma unroll
     for (int v = 0; v < NV; ++v) {
@@ -319,18 +337,29 @@ ln_bwd_warp_kernel(const T* __restrict__ dy, const T* __restrict__ x, const floa
         unpack8<T>(gr[v], df);
         const float4 g0 = __ldg(reinterpret_cast<const float4*>(gamma + c)), g1 = __ldg(reinterpret_cast<const float4*>(gamma + c + 4));
         const float gg[8] = {g0.x, g0.y, g0.z, g0.w, g1.x, g1.y, g1.z, g1.w};
+        float4* pg = reinterpret_cast<float4*>(wdg + c);
+        float4* pb = reinterpret_cast<float4*>(wdb + c);
+        float4 a0 = pg[0], a1 = pg[1], b0 = pb[0], b1 = pb[1];
+        float ag[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w};
+        float ab[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
 #pragma unroll
         for (int i = 0; i < 8; ++i) {
-          const float xhat = (xf[i] - mu) * rs;
-          dg[v][i] += df[i] * xhat;
-          db[v][i] += df[i];
+          const float xhat = fmaf(xf[i], rs, nmr);
+          ag[i] = fmaf(df[i], xhat, ag[i]);
+          ab[i] += df[i];
           const float g = df[i] * gg[i];
           s1 += g;
-          s2 += g * xhat;
+          s2 = fmaf(g, xhat, s2);
         }
+        pg[0] = make_float4(ag[0], ag[1], ag[2], ag[3]);
+        pg[1] = make_float4(ag[4], ag[5], ag[6], ag[7]);
+        pb[0] = make_float4(ab[0], ab[1], ab[2], ab[3]);
+        pb[1] = make_float4(ab[4], ab[5], ab[6], ab[7]);
       }
     }
     const float m1 = warp_sum(s1) * inv_h, m2 = warp_sum(s2) * inv_h;
+    // dx = rs * (dy * gamma - m1 - xhat * m2) = dy * (rs * gamma) + x * kx + k0
+    const float kx = -rs * rs * m2, k0 = rs * (mu * rs * m2 - m1);
 #pragma unroll
     for (int v = 0; v < NV; ++v) {
       const int c = (v * 32 + lane) * 8;
@@ -341,7 +370,7 @@ ln_bwd_warp_kernel(const T* __restrict__ dy, const T* __restrict__ x, const floa
         const float4 g0 = __ldg(reinterpret_cast<const float4*>(gamma + c)), g1 = __ldg(reinterpret_cast<const float4*>(gamma + c + 4));
         const float gg[8] = {g0.x, g0.y, g0.z, g0.w, g1.x, g1.y, g1.z, g1.w};
 #pragma unroll
-        for (int i = 0; i < 8; ++i) o[i] = (df[i] * gg[i] - m1 - (xf[i] - mu) * rs * m2) * rs;
+        for (int i = 0; i < 8; ++i) o[i] = fmaf(df[i], rs * gg[i], fmaf(xf[i], kx, k0));
         if (HAS_RES) {
           float rf[8];
           unpack8<T>(*reinterpret_cast<const uint4*>(dres + base + c), rf);
@@ -353,22 +382,30 @@ ln_bwd_warp_kernel(const T* __restrict__ dy, const T* __restrict__ x, const floa
     }
   }
   __syncthreads();
-#pragma unroll
-  for (int v = 0; v < NV; ++v) {
-    const int c = (v * 32 + lane) * 8;
-    if (c < H) {
-#pragma unroll
-      for (int i = 0; i < 8; ++i) {
-        atomicAdd(&sacc[c + i], dg[v][i]);
-        atomicAdd(&sacc[H + c + i], db[v][i]);
-      }
-    }
-  }
-  __syncthreads();
   for (int i = threadIdx.x; i < H; i += blockDim.x) {
-    part_dgamma[static_cast<size_t>(blockIdx.x) * H + i] = sacc[i];
-    part_dbeta[static_cast<size_t>(blockIdx.x) * H + i] = sacc[H + i];
+    float a = 0.f, b = 0.f;
+#pragma unroll
+    for (int w = 0; w < kWarpRows; ++w) {
+      a += sacc[static_cast<size_t>(w) * 2 * H + i];
+      b += sacc[static_cast<size_t>(w) * 2 * H + H + i];
+    }
+    part_dgamma[static_cast<size_t>(blockIdx.x) * H + i] = a;
+    part_dbeta[static_cast<size_t>(blockIdx.x) * H + i] = b;
   }
+}
+
+template <typename T, int NV, bool HAS_RES>
+static void launch_ln_bwd_warp(int grid, size_t smem, cudaStream_t stream, const void* dy, const void* x, const float* mean,
+                               const float* rstd, const float* gamma, const void* dres, void* dx, float* pdg, float* pdb,
+                               int rows, int H) {
+  auto kern = ln_bwd_warp_kernel<T, NV, HAS_RES>;
+  static bool done = false;
+  if (!done) {
+    C10_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kWarpRows * 2 * 2048 * 4));
+    done = true;
+  }
+  kern<<<grid, 32 * kWarpRows, smem, stream>>>(reinterpret_cast<const T*>(dy), reinterpret_cast<const T*>(x), mean, rstd, gamma,
+                                               reinterpret_cast<const T*>(dres), reinterpret_cast<T*>(dx), pdg, pdb, rows, H);
 }
 
 // out[c] = sum_p part[p, c] for two partial buffers at once.
@@ -624,21 +661,19 @@ std::vector<torch::Tensor> layer_norm_bwd_res(torch::Tensor dy, torch::Tensor x,
   if (rows == 0) return {dx, dgamma, dbeta};
   auto stream = at::cuda::getCurrentCUDAStream();
   const int sms = at::cuda::getCurrentDeviceProperties()->multiProcessorCount;
-  const int grid = std::max(1, std::min((rows + kWarpRows - 1) / kWarpRows, sms));
+  const int grid = std::max(1, std::min((rows + kWarpRows - 1) / kWarpRows, 2 * sms));
   auto scratch = torch::empty({2, grid, H}, f32);
   float* pdg = scratch.data_ptr<float>();
   float* pdb = pdg + static_cast<size_t>(grid) * H;
-  const size_t smem = 2 * static_cast<size_t>(H) * sizeof(float);
+  const size_t smem = static_cast<size_t>(kWarpRows) * 2 * H * sizeof(float);
   if (has_res) {
-    DISPATCH_16_NV(x, ln_bwd_warp_kernel<T, NV, true><<<grid, 32 * kWarpRows, smem, stream>>>(
-                          reinterpret_cast<const T*>(dy.data_ptr()), reinterpret_cast<const T*>(x.data_ptr()),
-                          mean.data_ptr<float>(), rstd.data_ptr<float>(), gamma.data_ptr<float>(),
-                          reinterpret_cast<const T*>(dres->data_ptr()), reinterpret_cast<T*>(dx.data_ptr()), pdg, pdb, rows, H);)
+    DISPATCH_16_NV(x, (launch_ln_bwd_warp<T, NV, true>(grid, smem, stream, dy.data_ptr(), x.data_ptr(), mean.data_ptr<float>(),
+                                                       rstd.data_ptr<float>(), gamma.data_ptr<float>(), dres->data_ptr(),
+                                                       dx.data_ptr(), pdg, pdb, rows, H));)
   } else {
-    DISPATCH_16_NV(x, ln_bwd_warp_kernel<T, NV, false><<<grid, 32 * kWarpRows, smem, stream>>>(
-                          reinterpret_cast<const T*>(dy.data_ptr()), reinterpret_cast<const T*>(x.data_ptr()),
-                          mean.data_ptr<float>(), rstd.data_ptr<float>(), gamma.data_ptr<float>(), nullptr,
-                          reinterpret_cast<T*>(dx.data_ptr()), pdg, pdb, rows, H);)
+    DISPATCH_16_NV(x, (launch_ln_bwd_warp<T, NV, false>(grid, smem, stream, dy.data_ptr(), x.data_ptr(), mean.data_ptr<float>(),
+                                                        rstd.data_ptr<float>(), gamma.data_ptr<float>(), nullptr, dx.data_ptr(),
+                                                        pdg, pdb, rows, H));)
   }
   C10_CUDA_KERNEL_LAUNCH_CHECK();
   colsum2_kernel<<<(H + 255) / 256, 256, 0, stream>>>(pdg, pdb, dgamma.data_ptr<float>(), dbeta.data_ptr<float>(), grid, H);
