@@ -158,6 +158,16 @@ __global__ void __launch_bounds__(256) act_bwd_kernel(const T* __restrict__ dy, 
   int r = r0;
   for (; r + 1 < r1; r += 2) {
     const size_t off0 = static_cast<size_t>(r) * N + c, off1 = off0 + N;
+    if (r + 9 < r1) {
+      // the rows this thread reads four iterations from now go to L2 (costs no registers)
+      const size_t offp = off0 + static_cast<size_t>(8) * N;
+      asm volatile("prefetch.global.L2 [%0];" ::"l"(dy + offp));
+      asm volatile("prefetch.global.L2 [%0];" ::"l"(dy + offp + N));
+      if (ACT != 0) {
+        asm volatile("prefetch.global.L2 [%0];" ::"l"(z + offp));
+        asm volatile("prefetch.global.L2 [%0];" ::"l"(z + offp + N));
+      }
+    }
     Vec8<T> vd0, vd1, vz0, vz1;
     vd0.load(dy + off0);
     vd1.load(dy + off1);

@@ -224,6 +224,18 @@ ln_fwd_warp_kernel(const T* __restrict__ x, const T* __restrict__ res, const flo
       const int c = (v * 32 + lane) * 8;
       raw[v] = c < H ? *reinterpret_cast<const uint4*>(x + base + c) : make_uint4(0, 0, 0, 0);
     }
+    // the next row of this warp goes to L2 while this one is processed (costs no registers)
+    if (row + nwarps < rows) {
+      const size_t nbase = static_cast<size_t>(row + nwarps) * H;
+#pragma unroll
+      for (int v = 0; v < NV; ++v) {
+        const int c = (v * 32 + lane) * 8;
+        if (c < H) {
+          asm volatile("prefetch.global.L2 [%0];" ::"l"(x + nbase + c));
+          if (HAS_RES) asm volatile("prefetch.global.L2 [%0];" ::"l"(res + nbase + c));
+        }
+      }
+    }
     if (HAS_RES) {
 #pragma unroll
       for (int v = 0; v < NV; ++v) {
