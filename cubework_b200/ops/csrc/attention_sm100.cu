@@ -822,18 +822,39 @@ __global__ void attn_pack_kernel(const T* __restrict__ src, T* __restrict__ dst,
 }
 
 // delta[b, h, t] = sum_d dO[b,t,h,d] * O[b,t,h,d]
+// A warp takes 32 consecutive (b, t, h) rows, i.e. 32 * dh consecutive elements of both tensors: it reads them with
+// coalesced 16-byte loads (the chunk starts on a 16-byte boundary for every dh), leaves the products in shared memory
+// and each lane sums one row.
 template <typename T>
 __global__ void attn_delta_kernel(const T* __restrict__ dout, const T* __restrict__ out, float* __restrict__ delta, int B,
                                   int Tn, int H, int dh) {
-  const int64_t idx = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
-  if (idx >= static_cast<int64_t>(B) * Tn * H) return;
+  extern __shared__ __align__(16) uint8_t delta_smem[];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  float* prod = reinterpret_cast<float*>(delta_smem) + static_cast<size_t>(warp) * 32 * dh;
+  const int64_t total = static_cast<int64_t>(B) * Tn * H;
+  const int64_t first = static_cast<int64_t>(blockIdx.x) * blockDim.x + warp * 32;
+  if (first >= total) return;
+  const int rows = static_cast<int>(min(static_cast<int64_t>(32), total - first));
+  const int n_el = rows * dh;
+  const T* a = dout + first * dh;
+  const T* o = out + first * dh;
+  const int n16 = n_el / 8;
+  for (int i = lane; i < n16; i += 32) {
+    const uint4 va = reinterpret_cast<const uint4*>(a)[i], vo = reinterpret_cast<const uint4*>(o)[i];
+    const T* ha = reinterpret_cast<const T*>(&va);
+    const T* ho = reinterpret_cast<const T*>(&vo);
+#pragma unroll
+    for (int e = 0; e < 8; ++e) prod[i * 8 + e] = to_f(ha[e]) * to_f(ho[e]);
+  }
+  for (int i = n16 * 8 + lane; i < n_el; i += 32) prod[i] = to_f(a[i]) * to_f(o[i]);
+  __syncwarp();
+  if (lane >= rows) return;
+  float s = 0.f;
+  for (int d = 0; d < dh; ++d) s += prod[lane * dh + d];
+  const int64_t idx = first + lane;
   const int h = idx % H;
   const int64_t bt = idx / H;
   const int t = bt % Tn, b = bt / Tn;
-  const T* a = dout + idx * dh;
-  const T* o = out + idx * dh;
-  float s = 0.f;
-  for (int d = 0; d < dh; ++d) s += to_f(a[d]) * to_f(o[d]);
   delta[(static_cast<int64_t>(b) * H + h) * Tn + t] = s;
 }
 
@@ -850,16 +871,24 @@ __global__ void attn_dq_store_kernel(const float* __restrict__ dq_acc, T* __rest
   const int64_t first = static_cast<int64_t>(blockIdx.x) * blockDim.x + warp * 32;
   if (first >= total) return;
   const int rows = static_cast<int>(min(static_cast<int64_t>(32), total - first));
-  if (lane < rows) {
-    const int64_t bth = first + lane;
-    const int h = bth % H;
-    const int64_t bt = bth / H;
-    const int t = bt % Tn, b = bt / Tn;
-    const float4* srow = reinterpret_cast<const float4*>(dq_acc + ((static_cast<int64_t>(b) * H + h) * Tn + t) * DP);
-    for (int q = 0; q < DP / 4; ++q) {
-      const float4 v = srow[q];
-      T* o = stage + lane * DP + q * 4;
-      o[0] = from_f<T>(v.x); o[1] = from_f<T>(v.y); o[2] = from_f<T>(v.z); o[3] = from_f<T>(v.w);
+  // eight lanes read one accumulator row (DP floats, contiguous), so an instruction touches four rows' full lines
+  // instead of 16 bytes of 32 different ones
+  {
+    const int sub = lane >> 3, qv = lane & 7;
+    for (int r0 = 0; r0 < rows; r0 += 4) {
+      const int rr = r0 + sub;
+      if (rr < rows) {
+        const int64_t bth = first + rr;
+        const int h = bth % H;
+        const int64_t bt = bth / H;
+        const int t = bt % Tn, b = bt / Tn;
+        const float4* srow = reinterpret_cast<const float4*>(dq_acc + ((static_cast<int64_t>(b) * H + h) * Tn + t) * DP);
+        for (int q = qv; q < DP / 4; q += 8) {
+          const float4 v = srow[q];
+          T* o = stage + rr * DP + q * 4;
+          o[0] = from_f<T>(v.x); o[1] = from_f<T>(v.y); o[2] = from_f<T>(v.z); o[3] = from_f<T>(v.w);
+        }
+      }
     }
   }
   __syncwarp();
@@ -1942,12 +1971,13 @@ torch::Tensor attention_bwd(torch::Tensor dout, torch::Tensor qkv, torch::Tensor
   auto dq_acc = torch::zeros({dq_elems + 32}, f32);
   auto stream = at::cuda::getCurrentCUDAStream();
   const int64_t rows = static_cast<int64_t>(p.B) * p.T * p.H;
+  const int dthreads = p.dh > 64 ? 64 : 128;       // 4 * dh bytes of shared memory per thread, 48 KB per CTA at most
   if (p.is_bf16) {
-    attn_delta_kernel<__nv_bfloat16><<<(rows + 255) / 256, 256, 0, stream>>>(
+    attn_delta_kernel<__nv_bfloat16><<<(rows + dthreads - 1) / dthreads, dthreads, dthreads * p.dh * 4, stream>>>(
         reinterpret_cast<const __nv_bfloat16*>(dout.data_ptr()), reinterpret_cast<const __nv_bfloat16*>(out.data_ptr()),
         delta.data_ptr<float>(), p.B, p.T, p.H, p.dh);
   } else {
-    attn_delta_kernel<__half><<<(rows + 255) / 256, 256, 0, stream>>>(
+    attn_delta_kernel<__half><<<(rows + dthreads - 1) / dthreads, dthreads, dthreads * p.dh * 4, stream>>>(
         reinterpret_cast<const __half*>(dout.data_ptr()), reinterpret_cast<const __half*>(out.data_ptr()),
         delta.data_ptr<float>(), p.B, p.T, p.H, p.dh);
   }
