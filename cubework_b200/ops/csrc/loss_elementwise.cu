@@ -191,12 +191,26 @@ __global__ void __launch_bounds__(256) act_bwd_kernel(const T* __restrict__ dy, 
   }
 }
 
-__global__ void colsum1_kernel(const float* __restrict__ part, float* __restrict__ out, int P, int N) {
-  const int c = blockIdx.x * blockDim.x + threadIdx.x;
-  if (c >= N) return;
-  float a = 0.f;
-  for (int p = 0; p < P; ++p) a += part[static_cast<size_t>(p) * N + c];
-  out[c] = a;
+// out[c] = sum_p part[p, c].  A CTA of 64 columns x 4 row groups: every thread keeps four loads in flight, the row
+// groups meet in shared memory (one thread per column over all P rows left a handful of CTAs waiting on one load each).
+__global__ void __launch_bounds__(256) colsum1_kernel(const float* __restrict__ part, float* __restrict__ out, int P, int N) {
+  __shared__ float red[4][64];
+  const int tx = threadIdx.x & 63, ty = threadIdx.x >> 6;
+  const int c = blockIdx.x * 64 + tx;
+  float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
+  if (c < N) {
+    int p = ty;
+    for (; p + 12 < P; p += 16) {
+      a0 += part[static_cast<size_t>(p) * N + c];
+      a1 += part[static_cast<size_t>(p + 4) * N + c];
+      a2 += part[static_cast<size_t>(p + 8) * N + c];
+      a3 += part[static_cast<size_t>(p + 12) * N + c];
+    }
+    for (; p < P; p += 4) a0 += part[static_cast<size_t>(p) * N + c];
+  }
+  red[ty][tx] = (a0 + a1) + (a2 + a3);
+  __syncthreads();
+  if (ty == 0 && c < N) out[c] = (red[0][tx] + red[1][tx]) + (red[2][tx] + red[3][tx]);
 }
 
 // ---- embedding -------------------------------------------------------------------------------------------------
@@ -313,7 +327,7 @@ std::vector<torch::Tensor> act_backward(torch::Tensor dy, c10::optional<torch::T
 #undef LAUNCH_ACT
   C10_CUDA_KERNEL_LAUNCH_CHECK();
   if (want_sum) {
-    colsum1_kernel<<<(N + 255) / 256, 256, 0, stream>>>(partials.data_ptr<float>(), db.data_ptr<float>(), gy, N);
+    colsum1_kernel<<<(N + 63) / 64, 256, 0, stream>>>(partials.data_ptr<float>(), db.data_ptr<float>(), gy, N);
     C10_CUDA_KERNEL_LAUNCH_CHECK();
   }
   return {dz, db};
