@@ -9,9 +9,10 @@
 //                     memory as 16-bit in the MMA's swizzled layout
 //   O_blk = P V       tcgen05.mma, V consumed as an MN-major operand straight from its row-major image
 //   O = O*alpha+O_blk in registers
-// Backward, one CTA per (128-key block, head, batch) looping over query blocks: S and dP = dO V^T in TMEM,
+// Backward, one work item per (128-key block, head, batch) looping over query blocks: S and dP = dO V^T in TMEM,
 // P / dS written to shared memory, dV += P^T dO and dK += dS^T Q accumulate in TMEM across the loop,
-// dQ = dS K is added to an fp32 scratch buffer with red.add (several key blocks contribute to one query block).
+// dQ = dS K is added to an fp32 scratch buffer (several key blocks contribute to one query block).  Head dims up
+// to 64 run as a persistent warp-specialised kernel (attn_bwd_ws_kernel), larger ones with one CTA per work item.
 //
 // Head dims are zero-padded to DP in {32, 64, 96, 128}.  Q / K / V / dO tiles arrive by TMA (4-D maps over
 // [dh, T, heads, B] with a 64 x 128 box, 128-byte swizzle; columns past dh and rows past T are zero-filled by
